@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the WKV6 hot path: forward + backward at B8 T4096 H32 N64 bf16 (fp32 u, fp32 state).
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N --steps K ...  # the reference algorithm on the host cores
+
+One "step" is one forward plus one backward of the operator over one batch of seeded synthetic inputs
+(r,k,v ~ N(0,1)/sqrt(N), w ~ U(-6,1), u ~ N(0,0.1), gy ~ N(0,1)).  Every rank runs the full workload on
+its own GPU (weak scaling: the (batch, head) pairs are independent, so there is no data-path collective);
+``--scaling strong`` instead splits the B rows of the one workload across the ranks.
+
+Rank 0 prints one JSON line.  ``value`` is device-resident throughput (CUDA events, max over ranks);
+``e2e`` is the same step driven through ``RWKVKernelOperator`` from pinned host buffers with the host<->device
+copies inside the timed region; ``roofline`` relates the dominant kernel to the measured HBM copy bandwidth;
+``cpu_baseline`` is the C restatement of the reference algorithm timed on the host cores on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "wkv6_fwd_bwd_mtokens_per_s"
+UNIT = "Mtokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--variant", default="auto", choices=["auto", "seq", "chunk"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--B", type=int, default=8)
+    ap.add_argument("--T", type=int, default=4096)
+    ap.add_argument("--H", type=int, default=32)
+    ap.add_argument("--N", type=int, default=64)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-heads", type=int, default=0, help="(b,h) pairs in the CPU sample; 0 = auto")
+    return ap.parse_args()
+
+
+def workload_name(a):
+    return f"wkv6 fwd+bwd B{a.B} T{a.T} H{a.H} N{a.N} {a.dtype}"
+
+
+# ---- CPU baseline / reference arm -----------------------------------------------------------------
+
+def cpu_fwd_bwd(a, pairs, reps):
+    """Time the C restatement (fp32, all host threads) on `pairs` (b,h) sequences of full length T."""
+    from oracle import c_oracle
+    from oracle.wkv6_oracle import make_inputs
+    d = make_inputs(1, a.T, pairs, a.N, seed=1)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        c_oracle.fwd(d["r"], d["k"], d["v"], d["w"], d["u"], a.N, dtype=np.float32)
+        c_oracle.bwd(d["r"], d["k"], d["v"], d["w"], d["u"], d["gy"], a.N, dtype=np.float32)
+        times.append(time.perf_counter() - t0)
+    return times, c_oracle.threads()
+
+
+def pick_sample(a, budget_s):
+    """Number of (b,h) sequences per CPU step: the whole workload if it fits the time budget, else a
+    multiple of the thread count that does."""
+    from oracle import c_oracle
+    threads = c_oracle.threads()
+    if a.cpu_sample_heads:
+        return a.cpu_sample_heads, threads
+    probe = max(threads, 8)
+    t_probe, _ = cpu_fwd_bwd(a, probe, 2)
+    per_pair = min(t_probe) / probe
+    total = a.B * a.H
+    if per_pair * total <= budget_s:
+        return total, threads
+    pairs = max(threads, int(budget_s / per_pair) // threads * threads)
+    return min(pairs, total), threads
+
+
+def sample_text(a, pairs):
+    whole = "the whole workload: " if pairs == a.B * a.H else ""
+    return (f"{whole}{pairs} of {a.B * a.H} (batch,head) sequences at full T={a.T}, fp32; "
+            "C restatement of the reference loop, OpenMP over sequences")
+
+
+def cpu_baseline(a):
+    """Tokens/s on the host cores.  A token is one time step of all H heads, so P sequences of length T are
+    P*T/H tokens."""
+    pairs, threads = pick_sample(a, budget_s=4.0)
+    times, _ = cpu_fwd_bwd(a, pairs, 3)
+    best = min(times)
+    tokens = pairs * a.T / a.H
+    return {"value": tokens / best / 1e6, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": sample_text(a, pairs) + ", best of 3", "seconds_per_sample": best}
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    pairs, threads = pick_sample(a, budget_s=3.0)
+    times, _ = cpu_fwd_bwd(a, pairs, a.warmup + a.steps)
+    timed = times[a.warmup:]
+    tokens = pairs * a.T / a.H
+    total = sum(timed)
+    val = tokens * len(timed) / total / 1e6
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": 1e3 * total / len(timed), "higher_is_better": True,
+        "scaling": a.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "note": "reference algorithm on the host cores only"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample_text(a, pairs) + " per step"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- clocks ---------------------------------------------------------------------------------------
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                       "--format=csv,noheader,nounits", "-lms", "20"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.p is None:
+            return out
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.f.read().splitlines():
+            c = [x.strip() for x in ln.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])); mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, c[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        self.f.close()
+        os.unlink(self.f.name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ---- GPU arm --------------------------------------------------------------------------------------
+
+def run_b200(a):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != a.gpus and world > 1:
+        raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    import star_rwkv6_b200 as pkg
+    from star_rwkv6_b200 import _lib
+    from star_rwkv6_b200.rwkv_kernel.torch_rwkv_kernel import RWKVKernelOperator
+
+    B, T, H, N = a.B, a.T, a.H, a.N
+    if a.scaling == "strong" and world > 1:
+        assert (B * H) % world == 0
+        if B % world == 0:
+            B = B // world          # contiguous batch rows per rank
+        else:
+            H = (B * H // world) // B  # head shard per rank
+    C = H * N
+    xdt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    variant = _lib.VARIANTS[a.variant]
+
+    # seeded synthetic inputs, generated on the host; two rotating sets so consecutive steps do not reuse lines
+    g = torch.Generator().manual_seed(1234 + (rank if a.scaling == "strong" else 0))
+    nsets = 2
+    host, devs = [], []
+    for s in range(nsets):
+        hs = {
+            "r": (torch.randn(B, T, C, generator=g) / N ** 0.5).to(xdt).pin_memory(),
+            "k": (torch.randn(B, T, C, generator=g) / N ** 0.5).to(xdt).pin_memory(),
+            "v": (torch.randn(B, T, C, generator=g) / N ** 0.5).to(xdt).pin_memory(),
+            "w": (torch.rand(B, T, C, generator=g) * 7.0 - 6.0).to(xdt).pin_memory(),
+            "gy": torch.randn(B, T, C, generator=g).to(xdt).pin_memory(),
+        }
+        host.append(hs)
+        devs.append({n: t.to(dev) for n, t in hs.items()})
+    u_host = (torch.randn(H, N, generator=g) * 0.1).pin_memory()
+    u = u_host.to(dev)
+
+    resolved = pkg.ops.resolve_variant(devs[0]["r"], u, N, variant)
+    vname = {1: "seq", 2: "chunk"}[resolved]
+    launches_per_step = {"seq": 4, "chunk": 2}[vname]
+
+    def step(d):
+        y, _, ckpt = pkg.forward_raw(d["r"], d["k"], d["v"], d["w"], u, N, want_ckpt=True, variant=variant)
+        return y, ckpt
+
+    def step_bwd(d, ckpt):
+        return pkg.backward_raw(d["r"], d["k"], d["v"], d["w"], u, d["gy"], N, ckpt=ckpt, variant=variant)
+
+    # clocks are sampled from the warm-up on: the timed region itself can be shorter than one sampling period
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    for i in range(a.warmup):
+        d = devs[i % nsets]
+        y, ck = step(d)
+        step_bwd(d, ck)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(a.steps)]
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e_start.record()
+    for i in range(a.steps):
+        d = devs[i % nsets]
+        ev[i][0].record()
+        y, ck = step(d)
+        ev[i][1].record()
+        grads = step_bwd(d, ck)
+        ev[i][2].record()
+    e_stop.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = e_start.elapsed_time(e_stop)
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    if world > 1:
+        t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, fwd_ms, bwd_ms = t.tolist()
+    ms_per_step = total_ms / a.steps
+    tokens_per_step_global = B * T * world  # every rank processes B*T tokens of H heads
+    if a.scaling == "strong" and world > 1:
+        tokens_per_step_global = a.B * a.T
+    value = tokens_per_step_global / (ms_per_step * 1e-3) / 1e6
+
+    # e2e: through the operator, host buffers, copies inside the timed region
+    e2e = None
+    if not a.no_e2e:
+        op = RWKVKernelOperator(N, T, variant=a.variant)
+        ydt = xdt
+        out_host = {n: torch.empty(B, T, C, dtype=ydt).pin_memory() for n in ("y", "gr", "gk", "gv", "gw")}
+        gu_host = torch.empty(H, N, dtype=torch.float32).pin_memory()
+
+        def e2e_step(hs):
+            t = {n: hs[n].to(dev, non_blocking=True) for n in ("r", "k", "v", "w", "gy")}
+            ud = u_host.to(dev, non_blocking=True).requires_grad_(True)
+            for n in ("r", "k", "v", "w"):
+                t[n].requires_grad_(True)
+            y, _ = op(t["r"], t["k"], t["v"], t["w"], ud)
+            y.backward(t["gy"])
+            out_host["y"].copy_(y.detach(), non_blocking=True)
+            out_host["gr"].copy_(t["r"].grad, non_blocking=True)
+            out_host["gk"].copy_(t["k"].grad, non_blocking=True)
+            out_host["gv"].copy_(t["v"].grad, non_blocking=True)
+            out_host["gw"].copy_(t["w"].grad, non_blocking=True)
+            gu_host.copy_(ud.grad, non_blocking=True)
+
+        n_e2e = max(3, min(a.steps, 10))
+        for i in range(2):
+            e2e_step(host[i % nsets])
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for i in range(n_e2e):
+            e2e_step(host[i % nsets])
+        s1.record()
+        barrier()
+        e2e_ms = s0.elapsed_time(s1) / n_e2e
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = t.item()
+        esz = 2 if a.dtype == "bf16" else 4
+        e2e = {"value": tokens_per_step_global / (e2e_ms * 1e-3) / 1e6, "unit": UNIT,
+               "h2d_bytes_per_step": 5 * B * T * C * esz + H * N * 4,
+               "d2h_bytes_per_step": 5 * B * T * C * esz + H * N * 4,
+               "ms_per_step": e2e_ms, "steps": n_e2e, "api": "RWKVKernelOperator.__call__ + backward, pinned host buffers"}
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+        else:
+            peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+        esz = 2 if a.dtype == "bf16" else 4
+        elems = B * T * C
+        bwd_bytes, fwd_bytes = 9 * esz * elems, 5 * esz * elems
+        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        roofline = {
+            "bound": "hbm", "kernel": f"{vname} backward", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+            "algorithmic_bytes_per_launch": bwd_bytes, "avg_ms": bwd_ms,
+            "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
+                        "algorithmic_bytes_per_launch": fwd_bytes, "avg_ms": fwd_ms},
+            "step": {"achieved": (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9,
+                     "frac": (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9 / peak},
+        }
+        cpu = None if a.no_cpu_baseline else cpu_baseline(a)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": a.scaling, "vs_baseline": None,
+            "dtype": "bf16" if a.dtype == "bf16" else "f32", "data": "synthetic",
+            "config": {"workload": workload_name(a), "per_gpu": f"B{B} T{T} H{H} N{N}", "variant": vname,
+                       "u_dtype": "f32", "state": "f32",
+                       "l2": "two rotating input sets of 671 MB each, larger than the 126 MB L2",
+                       "parallelism": f"{world} independent ranks over (batch, head), no collective"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": launches_per_step * a.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_b200(a)
+
+
+if __name__ == "__main__":
+    main()

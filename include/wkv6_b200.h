@@ -1,0 +1,112 @@
+/*
+ * wkv6_b200 — C ABI of the B200 (sm_100a) RWKV-6 WKV recurrence.
+ *
+ * Plain pointers and sizes only; every function enqueues work on the CUDA
+ * stream it is given and returns without synchronising.  Nothing here
+ * allocates device memory: outputs, checkpoints and workspaces are the
+ * caller's.  All entry points return WKV6_OK (0) or a negative error code;
+ * wkv6_last_error() gives the message of the last failure on the calling
+ * thread.
+ *
+ * Tensor conventions
+ *   r, k, v, w, gy, y, gr, gk, gv, gw : [B, T, H*N], element (b, t, c) at
+ *        b*batch_stride + t*row_stride + c   (strides in elements; 0 selects the
+ *        dense value).  A head-sharded view of a wider tensor is expressed by a
+ *        row_stride larger than H*N, with no copy.
+ *   u    : [H, N]
+ *   gu   : [B, H, N]  per batch row; the caller sums over B, exactly as the
+ *        reference does outside its kernels.
+ *   state: S[b, h, key, value], N*N contiguous values per (b, h).  This is the
+ *        layout of the reference's non-CUDA operator
+ *        (rwkv_kernel/ops_rwkv_kernal.py:85-91).
+ *   y_t[j]   = sum_i r_t[i] * (u[i]*k_t[i]*v_t[j] + S_{t-1}[i][j])
+ *   S_t[i][j] = exp(-exp(w_t[i])) * S_{t-1}[i][j] + k_t[i]*v_t[j]
+ */
+#ifndef WKV6_B200_H_
+#define WKV6_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define WKV6_API __attribute__((visibility("default")))
+#else
+#define WKV6_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types.  Values equal the reference's gpu_ops::ElementType
+ * (rwkv_kernel/jax_kernel/kernels.h:30). */
+enum { WKV6_BF16 = 0, WKV6_F16 = 1, WKV6_F32 = 2 };
+
+/* Kernel variants.  AUTO picks per shape and dtype. */
+enum { WKV6_VARIANT_AUTO = 0, WKV6_VARIANT_SEQ = 1, WKV6_VARIANT_CHUNK = 2 };
+
+enum {
+    WKV6_OK = 0,
+    WKV6_ERR_INVALID = -1,     /* bad shape, dtype combination, null pointer, misalignment */
+    WKV6_ERR_UNSUPPORTED = -2, /* valid request that no compiled kernel covers */
+    WKV6_ERR_WORKSPACE = -3,   /* workspace / checkpoint buffer missing or too small */
+    WKV6_ERR_CUDA = -4         /* a CUDA runtime call failed; message carries cudaGetErrorString */
+};
+
+/* Problem description shared by all entry points.  Replaces the compile-time
+ * _N_/_T_ macros and the WKVDescriptor blob of the reference
+ * (rwkv_kernel/jax_kernel/kernels.h:24-42): N and T are runtime values. */
+typedef struct wkv6_problem {
+    int32_t B, T, H, N;   /* N (head size) in {8, 16, 32, 64}; the chunked variant needs N == 64 */
+    int32_t x_dtype;      /* r, k, v, w */
+    int32_t y_dtype;      /* y, gy, gr, gk, gv, gw.  Allowed (x, y): (F32,F32) (BF16,BF16) (F16,F32) (BF16,F32) */
+    int32_t u_dtype;      /* u: F32, or the same as x_dtype */
+    int32_t gu_dtype;     /* gu: F32 or y_dtype */
+    int32_t s_dtype;      /* s_in / s_out: F32 or BF16 */
+    int32_t variant;      /* WKV6_VARIANT_* */
+    int64_t row_stride;   /* elements between consecutive tokens; 0 = H*N */
+    int64_t batch_stride; /* elements between batch rows; 0 = T*row_stride */
+} wkv6_problem;
+
+WKV6_API const char *wkv6_last_error(void);
+WKV6_API const char *wkv6_version(void);
+
+/* Which variant AUTO resolves to for this problem (WKV6_VARIANT_SEQ / _CHUNK), or a negative error. */
+WKV6_API int wkv6_resolve_variant(const wkv6_problem *p);
+
+/*
+ * Forward.  Replaces kernel_forward / kernel_forward_state and their host launchers
+ * (rwkv_kernel/jax_kernel/rwkv_kernels.cu:107-203, 413-433; rwkv_kernel/torch_kernel/wkv6_cuda.cu:12-107, 323-339).
+ *   s_in   : optional [s_kinds, H, N, N] initial states (NULL = zero state)
+ *   s_map  : optional int64[B] device array, row b starts from s_in[s_map[b]]; NULL = identity when
+ *            s_kinds == B, all-zero when s_kinds == 1.  Values must lie in [0, s_kinds): the caller
+ *            validates them (the kernel clamps instead of trapping).
+ *   s_out  : optional [B, H, N, N] final states
+ *   ckpt   : optional checkpoint buffer of wkv6_ckpt_bytes(p) bytes.  When given, the forward stores what
+ *            the backward of the same variant needs so that it does not recompute it.
+ */
+WKV6_API int wkv6_forward(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
+                 const void *u, void *y, const void *s_in, const int64_t *s_map, int32_t s_kinds,
+                 void *s_out, void *ckpt, void *stream);
+
+WKV6_API size_t wkv6_ckpt_bytes(const wkv6_problem *p);
+
+/*
+ * Backward: gradients of sum(y*gy) with respect to r, k, v, w, u for a zero initial state; no gradient
+ * flows through a returned state.  Replaces kernel_backward_101/102/103/201 and HostApplyGradient
+ * (rwkv_kernel/jax_kernel/rwkv_kernels.cu:205-407, 435-444; rwkv_kernel/torch_kernel/wkv6_cuda.cu:112-314, 341-353).
+ * Every element of gr, gk, gv, gw, gu is written.
+ *   ckpt      : the buffer a forward of the same problem filled, or NULL (then the backward rebuilds it
+ *               inside the workspace)
+ *   workspace : wkv6_backward_workspace_bytes(p, ckpt != NULL) bytes of device scratch (may be NULL when 0)
+ */
+WKV6_API int wkv6_backward(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
+                  const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu,
+                  const void *ckpt, void *workspace, size_t workspace_bytes, void *stream);
+
+WKV6_API size_t wkv6_backward_workspace_bytes(const wkv6_problem *p, int have_ckpt);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WKV6_B200_H_ */

@@ -1,0 +1,70 @@
+"""ctypes binding of libwkv6_b200.so (the C ABI in include/wkv6_b200.h).
+
+The library is required: there is no CPU or framework fallback.  If it has not been built,
+importing this module raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libwkv6_b200.so")
+
+BF16, F16, F32 = 0, 1, 2
+VARIANT_AUTO, VARIANT_SEQ, VARIANT_CHUNK = 0, 1, 2
+VARIANTS = {"auto": VARIANT_AUTO, "seq": VARIANT_SEQ, "chunk": VARIANT_CHUNK}
+
+# every symbol include/wkv6_b200.h declares
+SYMBOLS = (
+    "wkv6_last_error", "wkv6_version", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
+    "wkv6_backward", "wkv6_backward_workspace_bytes",
+)
+
+
+class Problem(ctypes.Structure):
+    _fields_ = [
+        ("B", ctypes.c_int32), ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("N", ctypes.c_int32),
+        ("x_dtype", ctypes.c_int32), ("y_dtype", ctypes.c_int32), ("u_dtype", ctypes.c_int32),
+        ("gu_dtype", ctypes.c_int32), ("s_dtype", ctypes.c_int32), ("variant", ctypes.c_int32),
+        ("row_stride", ctypes.c_int64), ("batch_stride", ctypes.c_int64),
+    ]
+
+
+class WKV6Error(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"wkv6_b200 error {code}: {msg}")
+        self.code = code
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m star_rwkv6_b200.build` "
+            "(nvcc, sm_100a). There is no fallback path.")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, i64p, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t
+    pp = ctypes.POINTER(Problem)
+    lib.wkv6_last_error.restype = ctypes.c_char_p
+    lib.wkv6_last_error.argtypes = []
+    lib.wkv6_version.restype = ctypes.c_char_p
+    lib.wkv6_version.argtypes = []
+    lib.wkv6_resolve_variant.restype = ctypes.c_int
+    lib.wkv6_resolve_variant.argtypes = [pp]
+    lib.wkv6_forward.restype = ctypes.c_int
+    lib.wkv6_forward.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, i64p, i32, vp, vp, vp]
+    lib.wkv6_ckpt_bytes.restype = sz
+    lib.wkv6_ckpt_bytes.argtypes = [pp]
+    lib.wkv6_backward.restype = ctypes.c_int
+    lib.wkv6_backward.argtypes = [pp] + [vp] * 11 + [vp, vp, sz, vp]
+    lib.wkv6_backward_workspace_bytes.restype = sz
+    lib.wkv6_backward_workspace_bytes.argtypes = [pp, ctypes.c_int]
+    return lib
+
+
+lib = _load()
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise WKV6Error(rc, lib.wkv6_last_error().decode())
