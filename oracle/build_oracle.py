@@ -19,7 +19,7 @@ def build(force: bool = False) -> str:
     objs = []
     for real, suffix in (("double", "f64"), ("float", "f32")):
         obj = os.path.join(HERE, f"wkv6_oracle_{suffix}.o")
-        subprocess.check_call(["gcc", "-O3", "-march=native", "-fopenmp", "-fPIC", "-std=c11",
+        subprocess.check_call(["gcc", "-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-std=c11",
                                f"-DREAL={real}", f"-DSUFFIX={suffix}", "-c", SRC, "-o", obj])
         objs.append(obj)
     subprocess.check_call(["gcc", "-shared", "-fopenmp", "-o", LIB] + objs + ["-lm"])
