@@ -71,6 +71,11 @@ typedef struct wkv6_problem {
 WKV6_API const char *wkv6_last_error(void);
 WKV6_API const char *wkv6_version(void);
 
+/* Error word of the device kernels on the current device: 0, or the code of a bounded in-kernel wait that
+ * ran out (the kernel then unwinds and leaves its outputs undefined).  Synchronises the device.  The
+ * reference has no counterpart: its kernels contain no waits. */
+WKV6_API int wkv6_device_status(void);
+
 /* Which variant AUTO resolves to for this problem (WKV6_VARIANT_SEQ / _CHUNK), or a negative error. */
 WKV6_API int wkv6_resolve_variant(const wkv6_problem *p);
 

@@ -17,7 +17,7 @@ VARIANTS = {"auto": VARIANT_AUTO, "seq": VARIANT_SEQ, "chunk": VARIANT_CHUNK}
 
 # every symbol include/wkv6_b200.h declares
 SYMBOLS = (
-    "wkv6_last_error", "wkv6_version", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
+    "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
     "wkv6_backward", "wkv6_backward_workspace_bytes",
 )
 
@@ -40,7 +40,7 @@ class WKV6Error(RuntimeError):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m star_rwkv6_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python star_rwkv6_b200/build.py` "
             "(nvcc, sm_100a). There is no fallback path.")
     lib = ctypes.CDLL(LIB_PATH)
     vp, i32, i64p, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t
@@ -49,6 +49,8 @@ def _load():
     lib.wkv6_last_error.argtypes = []
     lib.wkv6_version.restype = ctypes.c_char_p
     lib.wkv6_version.argtypes = []
+    lib.wkv6_device_status.restype = ctypes.c_int
+    lib.wkv6_device_status.argtypes = []
     lib.wkv6_resolve_variant.restype = ctypes.c_int
     lib.wkv6_resolve_variant.argtypes = [pp]
     lib.wkv6_forward.restype = ctypes.c_int

@@ -1,6 +1,6 @@
 """Build the CUDA library in-tree: star_rwkv6_b200/libwkv6_b200.so (sm_100a only).
 
-``python -m star_rwkv6_b200.build`` compiles every ``.cu`` under ``csrc/`` with nvcc and links
+``python star_rwkv6_b200/build.py`` (run as a script, so that it works before the library exists) compiles every ``.cu`` under ``csrc/`` with nvcc and links
 one shared object that exports the C ABI declared in ``include/wkv6_b200.h``.  nvcc
 cross-compiles, so no GPU is needed to build.
 """

@@ -1,0 +1,422 @@
+// Chunked WKV6 forward for sm_100a: TMA-fed tcgen05 MMAs over 64-token chunks, fp32 state carried in
+// registers across the chunks of one (batch, head) sequence.
+//
+// Per chunk (tokens t, s in [0,64), key channel i, value channel j, c_t = sum_{sigma<=t} log d_sigma):
+//   A[t][s]  = sum_i r_t[i] k_s[i] exp(c_{t-1}[i] - c_s[i])      (s < t),   A[t][t] = sum_i r_t[i] u[i] k_t[i]
+//   y_t      = sum_s A[t][s] v_s  +  sum_i r_t[i] exp(c_{t-1}[i]) S_in[i][:]
+//   S_out    = diag(exp(c_63)) S_in + sum_s (k_s exp(c_63 - c_s)) (x) v_s
+// The decay exponent of A is split between the two bf16 operands around reference points so that no factor
+// can overflow: tokens are grouped in blocks of 16, each block I has the reference rho_I = its 8th token, and
+//   r~_t = r_t exp(c_{t-1} - c_rho(I)),   k~_s = k_s exp(c_rho(J) - c_s),
+//   A_IJ = r~_I (k~_J exp(c_rho(I) - c_rho(J)))^T        for block pairs J <= I.
+// Positive exponents span at most 8 steps; log-decays are clamped at -10 per step (a decay of e^-10, below
+// bf16 resolution of anything it multiplies), so every factor stays below e^80.  The block-pair factor is
+// folded into extra copies of k~ (one per block distance 1..3), all multiplied by the same r~ in one MMA;
+// the epilogue picks, per block pair, the columns of the matching copy.
+//
+// Tensor-memory map (256 columns, M = 64 accumulators occupy 16 lanes of each 32-lane quarter):
+//   lanes  0-15: cols [0,64) A for distance 0 | [64,128) y | [128,192) K^T V (state increment)
+//   lanes 16-31: cols [0,48) A distance 1 | [48,80) distance 2 | [80,96) distance 3
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "sm100_ptx.cuh"
+#include "wkv6_seq.cuh"
+
+namespace wkv6 {
+
+constexpr int kChunk = 64;
+constexpr int kTile = 8192;  // one [64 x 64] bf16 tile
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kMinLogDecay2 = -10.0f * 1.4426950408889634f;  // clamp of the per-step log2 decay
+
+// device-side error word: 0 = fine, otherwise the code of the wait that ran out
+__device__ int g_chunk_status;
+
+struct ChunkFwdSmem {
+    static constexpr int kStage = 4 * kTile;                 // r, k, v, w
+    static constexpr int oStage0 = 0;
+    static constexpr int oKH = 2 * kStage;                   // k^ (decayed to the chunk end), MN-major A operand
+    static constexpr int oKD = oKH + kTile;                  // k~ copies for block distances 1..3: 96 rows
+    static constexpr int oAM = oKD + 96 * 128;               // masked A (bf16), later the y tile
+    static constexpr int oSB = oAM + kTile;                  // bf16 copy of the state, MN-major B operand
+    static constexpr int oHead = oSB + kTile;                // float [4][64]: log-decay sum of the first 8 tokens of a block
+    static constexpr int oTot = oHead + 4 * 64 * 4;          // float [4][64]: log-decay sum of the block
+    static constexpr int oDtot = oTot + 4 * 64 * 4;          // float [64]: decay over the whole chunk
+    static constexpr int oBonus = oDtot + 64 * 4;            // float [64]: sum_i r u k per token
+    static constexpr int oBar = oBonus + 64 * 4;             // mbarriers: full[2], mma1, mma2
+    static constexpr int oSlot = oBar + 4 * 8;
+    static constexpr int kBytes = oSlot + 16;
+    static constexpr int kAlloc = kBytes + 1024;             // slack for the 1024-byte alignment of the base
+};
+
+struct ChunkFwdArgs {
+    const void *u; int u_dtype;
+    const void *s_in; const int64_t *s_map; int s_kinds; int s_dtype; void *s_out;
+    __nv_bfloat16 *ckpt;  // optional [B*H][T/64][64*64] bf16 chunk-start states in operand (swizzled) layout
+    int B, T, H;
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float2 ld_bf2(const uint8_t *p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+}
+__device__ __forceinline__ void st_bf2(uint8_t *p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(a, b);
+}
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+__global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_r,
+                                                        const __grid_constant__ CUtensorMap tm_k,
+                                                        const __grid_constant__ CUtensorMap tm_v,
+                                                        const __grid_constant__ CUtensorMap tm_w,
+                                                        const __grid_constant__ CUtensorMap tm_y,
+                                                        const ChunkFwdArgs a) {
+    using namespace ptx;
+    using SM = ChunkFwdSmem;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *sKH = smem + SM::oKH, *sKD = smem + SM::oKD, *sAM = smem + SM::oAM, *sSB = smem + SM::oSB;
+    float *sHead = reinterpret_cast<float *>(smem + SM::oHead);
+    float *sTot = reinterpret_cast<float *>(smem + SM::oTot);
+    float *sDtot = reinterpret_cast<float *>(smem + SM::oDtot);
+    float *sBonus = reinterpret_cast<float *>(smem + SM::oBonus);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SM::oBar);
+    uint64_t *bar_full = bars, *bar_mma1 = bars + 2, *bar_mma2 = bars + 3;
+    uint32_t *slot = reinterpret_cast<uint32_t *>(smem + SM::oSlot);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
+    const int nchunks = (a.T + kChunk - 1) / kChunk;
+    const int q = lane & 3, r0 = lane >> 2;  // accumulator fragment coordinates
+
+    if (tid == 0) {
+        mbar_init(&bar_full[0], 1);
+        mbar_init(&bar_full[1], 1);
+        mbar_init(bar_mma1, 1);
+        mbar_init(bar_mma2, 1);
+        fence_mbar_init();
+        prefetch_tensormap(&tm_r); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_w); prefetch_tensormap(&tm_y);
+    }
+    if (warp == 0) {
+        tmem_alloc(slot, 256);
+        tmem_relinquish();
+    }
+
+    // state in accumulator-fragment layout: rows i = 16*warp + r0 (+8), columns j = 8n + 2q (+1)
+    float S[32];
+    {
+        const bool has = a.s_in != nullptr;
+        size_t so = 0;
+        if (has) {
+            int64_t kind = a.s_map ? a.s_map[b] : (a.s_kinds == 1 ? 0 : b);
+            kind = kind < 0 ? 0 : (kind >= a.s_kinds ? a.s_kinds - 1 : kind);
+            so = ((size_t)kind * a.H + h) * 4096;
+        }
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = 16 * warp + r0 + (e >= 2 ? 8 : 0), j = 8 * n + 2 * q + (e & 1);
+                S[4 * n + e] = has ? load_any(a.s_in, a.s_dtype, so + (size_t)i * 64 + j) : 0.f;
+            }
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const int i0 = 16 * warp + r0, j = 8 * n + 2 * q;
+            *reinterpret_cast<uint32_t *>(sSB + sw128_off(i0, j)) = pack_bf2(S[4 * n], S[4 * n + 1]);
+            *reinterpret_cast<uint32_t *>(sSB + sw128_off(i0 + 8, j)) = pack_bf2(S[4 * n + 2], S[4 * n + 3]);
+        }
+    }
+    const float2 u2 = make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane),
+                                  load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane + 1));
+
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tb = *slot;
+    const uint32_t tmA0 = tb, tmY = tb + 64, tmS = tb + 128, tmAD = tb + (16u << 16);
+    const uint32_t wl = (uint32_t)(warp * 32) << 16;
+
+    auto issue_loads = [&](int c) {
+        const int st = c & 1;
+        uint8_t *base = smem + st * SM::kStage;
+        mbar_expect_tx(&bar_full[st], 4 * kTile);
+        tma_load_3d(base, &tm_r, &bar_full[st], h * 64, c * kChunk, b);
+        tma_load_3d(base + kTile, &tm_k, &bar_full[st], h * 64, c * kChunk, b);
+        tma_load_3d(base + 2 * kTile, &tm_v, &bar_full[st], h * 64, c * kChunk, b);
+        tma_load_3d(base + 3 * kTile, &tm_w, &bar_full[st], h * 64, c * kChunk, b);
+    };
+    if (tid == 0) {
+        issue_loads(0);
+        if (nchunks > 1) issue_loads(1);
+        if (a.ckpt != nullptr) {  // state at the start of chunk 0, already in operand layout
+            bulk_store(a.ckpt + (size_t)blockIdx.x * nchunks * 4096, sSB, kTile);
+            bulk_commit();
+        }
+    }
+
+    constexpr uint32_t idKK = umma_idesc_bf16(64, 64, false, false);
+    constexpr uint32_t idKK96 = umma_idesc_bf16(64, 96, false, false);
+    constexpr uint32_t idMM = umma_idesc_bf16(64, 64, true, true);
+    constexpr uint32_t idKM = umma_idesc_bf16(64, 64, false, true);
+
+    int err = 0;
+    int loads_pending = (nchunks > 1) ? 2 : 1;  // meaningful on thread 0 only
+    for (int c = 0; c < nchunks; ++c) {
+        const int st = c & 1;
+        uint8_t *sR = smem + st * SM::kStage, *sK = sR + kTile, *sV = sR + 2 * kTile, *sW = sR + 3 * kTile;
+        if (!mbar_wait(&bar_full[st], (c >> 1) & 1)) err = 1;
+        if (tid == 0) --loads_pending;
+
+        // ---- pass 1: per-step log2 decays of this thread's 16 tokens x 2 channels, inclusive running sums
+        float2 x[16];
+        {
+            float2 cs = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int tt = 0; tt < 16; ++tt) {
+                const int t = 16 * warp + tt;
+                const float2 w2 = ld_bf2(sW + sw128_off(t, 2 * lane));
+                float lx = fmaxf(-ex2f(w2.x * kLog2e) * kLog2e, kMinLogDecay2);
+                float ly = fmaxf(-ex2f(w2.y * kLog2e) * kLog2e, kMinLogDecay2);
+                if (c * kChunk + t >= a.T) { lx = 0.f; ly = 0.f; }
+                cs.x += lx; cs.y += ly;
+                x[tt] = cs;
+            }
+            *reinterpret_cast<float2 *>(&sHead[warp * 64 + 2 * lane]) = x[7];
+            *reinterpret_cast<float2 *>(&sTot[warp * 64 + 2 * lane]) = x[15];
+        }
+        // the previous chunk's y tile and checkpoint copies must have left shared memory before it is rewritten
+        if (tid == 0) bulk_wait_read<0>();
+        if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
+
+        // ---- pass 2: scaled operands
+        {
+            float2 pre = make_float2(0.f, 0.f), post = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int J = 0; J < 4; ++J) {
+                const float2 tj = *reinterpret_cast<const float2 *>(&sTot[J * 64 + 2 * lane]);
+                if (J < warp) { pre.x += tj.x; pre.y += tj.y; }
+                if (J > warp) { post.x += tj.x; post.y += tj.y; }
+            }
+            const float2 myhead = x[7], mytot = x[15];
+            const float2 tail = make_float2(mytot.x - myhead.x, mytot.y - myhead.y);
+            const float2 fR = make_float2(ex2f(myhead.x + pre.x), ex2f(myhead.y + pre.y));
+            const float2 fK = make_float2(ex2f(tail.x + post.x), ex2f(tail.y + post.y));
+            // factors of the k~ copies for block distances 1..3 (only those with warp + delta <= 3 exist)
+            float2 fD[3];
+            {
+                float2 acc = tail;
+#pragma unroll
+                for (int dl = 1; dl <= 3; ++dl) {
+                    const int Jt = warp + dl;  // the row block these copies serve
+                    if (Jt <= 3) {
+                        const float2 hj = *reinterpret_cast<const float2 *>(&sHead[Jt * 64 + 2 * lane]);
+                        const float2 tj = *reinterpret_cast<const float2 *>(&sTot[Jt * 64 + 2 * lane]);
+                        fD[dl - 1] = make_float2(ex2f(acc.x + hj.x), ex2f(acc.y + hj.y));
+                        acc.x += tj.x; acc.y += tj.y;
+                    } else {
+                        fD[dl - 1] = make_float2(0.f, 0.f);
+                    }
+                }
+            }
+            if (warp == 0) {
+                const float2 all = make_float2(mytot.x + post.x, mytot.y + post.y);
+                *reinterpret_cast<float2 *>(&sDtot[2 * lane]) = make_float2(ex2f(all.x), ex2f(all.y));
+            }
+            float bon[16];
+#pragma unroll
+            for (int tt = 0; tt < 16; ++tt) {
+                const int t = 16 * warp + tt;
+                const uint32_t off = sw128_off(t, 2 * lane);
+                const float2 xp = (tt == 0) ? make_float2(0.f, 0.f) : x[tt - 1];
+                const float2 er = make_float2(ex2f(xp.x - myhead.x), ex2f(xp.y - myhead.y));
+                const float2 ek = make_float2(ex2f(myhead.x - x[tt].x), ex2f(myhead.y - x[tt].y));
+                const float2 r2 = ld_bf2(sR + off), k2 = ld_bf2(sK + off);
+                bon[tt] = r2.x * u2.x * k2.x + r2.y * u2.y * k2.y;
+                const float2 rt = make_float2(r2.x * er.x, r2.y * er.y);
+                const float2 kt = make_float2(k2.x * ek.x, k2.y * ek.y);
+                st_bf2(sR + off, rt.x, rt.y);                       // r~  (A operand of the intra-chunk product)
+                st_bf2(sW + off, rt.x * fR.x, rt.y * fR.y);         // r^  (A operand against the incoming state)
+                st_bf2(sK + off, kt.x, kt.y);                       // k~  distance 0
+                st_bf2(sKH + off, kt.x * fK.x, kt.y * fK.y);        // k^  (state increment)
+                if (warp <= 2) st_bf2(sKD + off, kt.x * fD[0].x, kt.y * fD[0].y);                 // rows [0,48)
+                if (warp <= 1) st_bf2(sKD + 48 * 128 + off, kt.x * fD[1].x, kt.y * fD[1].y);      // rows [48,80)
+                if (warp == 0) st_bf2(sKD + 80 * 128 + off, kt.x * fD[2].x, kt.y * fD[2].y);      // rows [80,96)
+            }
+            // sum the bonus partials over the 32 channel pairs: 16 values across 32 lanes in 16 shuffles
+#pragma unroll
+            for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
+                const bool up = (lane & bit) != 0;
+#pragma unroll
+                for (int i2 = 0; i2 < half; ++i2) {
+                    const float send = up ? bon[i2] : bon[i2 + half];
+                    const float keep = up ? bon[i2 + half] : bon[i2];
+                    bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                }
+            }
+            bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 1);
+            if ((lane & 1) == 0) {
+                const int tok = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+                sBonus[16 * warp + tok] = bon[0];
+            }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncthreads();
+
+        if (tid == 0) {
+            tc_fence_after_sync();
+            const uint32_t aR = smem_u32(sR), aK = smem_u32(sK), aV = smem_u32(sV), aW = smem_u32(sW);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // A (distance 0) = r~ k~^T
+                umma_ss(tmA0, umma_desc_sw128(aR + 32 * kk), umma_desc_sw128(aK + 32 * kk), idKK, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // A (distances 1..3) = r~ [k~ copies]^T
+                umma_ss(tmAD, umma_desc_sw128(aR + 32 * kk), umma_desc_sw128(smem_u32(sKD) + 32 * kk), idKK96, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // state increment = k^^T v
+                umma_ss(tmS, umma_desc_sw128(smem_u32(sKH) + 2048 * kk), umma_desc_sw128(aV + 2048 * kk), idMM, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // y = r^ S_in
+                umma_ss(tmY, umma_desc_sw128(aW + 32 * kk), umma_desc_sw128(smem_u32(sSB) + 2048 * kk), idKM, kk > 0);
+            umma_commit(bar_mma1);
+        }
+        if (!mbar_wait(bar_mma1, c & 1)) err = 2;
+        tc_fence_after_sync();
+
+        // ---- epilogue of the intra-chunk matrix: pick, mask, round, store as the A operand of A v
+        {
+            const int I = warp;
+#pragma unroll
+            for (int J = 0; J < 4; ++J) {
+                uint32_t o0 = 0, o1 = 0, o2 = 0, o3 = 0;  // (row r0: cols 2q,2q+1 | 8+2q,..) and the same for row r0+8
+                if (J <= I) {
+                    const int dl = I - J;
+                    const uint32_t src = (dl == 0) ? (tmA0 + wl + 16 * J)
+                                                   : (tmAD + wl + (dl == 1 ? 16 * J : dl == 2 ? 48 + 16 * J : 80));
+                    uint32_t v8[8];
+                    tmem_ld_16x256b_x2(src, v8);
+                    tmem_wait_ld();
+                    float f[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v8[e]);
+                    if (dl == 0) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int row = r0 + ((e & 2) ? 8 : 0);
+                            const int col = 8 * (e >> 2) + 2 * q + (e & 1);
+                            f[e] = (col < row) ? f[e] : (col == row ? sBonus[16 * I + row] : 0.f);
+                        }
+                    }
+                    o0 = pack_bf2(f[0], f[1]); o2 = pack_bf2(f[2], f[3]);
+                    o1 = pack_bf2(f[4], f[5]); o3 = pack_bf2(f[6], f[7]);
+                }
+                const int t0r = 16 * I + r0, s0 = 16 * J + 2 * q;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r, s0)) = o0;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r, s0 + 8)) = o1;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r + 8, s0)) = o2;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r + 8, s0 + 8)) = o3;
+            }
+        }
+        // ---- state update in registers and its bf16 operand copy for the next chunk
+        {
+            uint32_t v32[32];
+            tmem_ld_16x256b_x8(tmS + wl, v32);
+            tmem_wait_ld();
+            const float d0 = sDtot[16 * warp + r0], d1 = sDtot[16 * warp + r0 + 8];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                S[4 * n + 0] = fmaf(S[4 * n + 0], d0, __uint_as_float(v32[4 * n + 0]));
+                S[4 * n + 1] = fmaf(S[4 * n + 1], d0, __uint_as_float(v32[4 * n + 1]));
+                S[4 * n + 2] = fmaf(S[4 * n + 2], d1, __uint_as_float(v32[4 * n + 2]));
+                S[4 * n + 3] = fmaf(S[4 * n + 3], d1, __uint_as_float(v32[4 * n + 3]));
+                const int i0 = 16 * warp + r0, j = 8 * n + 2 * q;
+                *reinterpret_cast<uint32_t *>(sSB + sw128_off(i0, j)) = pack_bf2(S[4 * n], S[4 * n + 1]);
+                *reinterpret_cast<uint32_t *>(sSB + sw128_off(i0 + 8, j)) = pack_bf2(S[4 * n + 2], S[4 * n + 3]);
+            }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        if (!__syncthreads_and(err == 0)) { err = err ? err : 11; break; }
+
+        if (tid == 0) {
+            tc_fence_after_sync();
+            // the state entering the next chunk is complete in shared memory: checkpoint it for the backward.
+            // Its read is drained (bulk_wait_read) before the next chunk's first barrier, ahead of the rewrite.
+            if (a.ckpt != nullptr && c + 1 < nchunks) {
+                bulk_store(a.ckpt + ((size_t)blockIdx.x * nchunks + c + 1) * 4096, sSB, kTile);
+                bulk_commit();
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // y += A v
+                umma_ss(tmY, umma_desc_sw128(smem_u32(sAM) + 32 * kk), umma_desc_sw128(smem_u32(sV) + 2048 * kk), idKM, true);
+            umma_commit(bar_mma2);
+        }
+        if (!mbar_wait(bar_mma2, c & 1)) err = 3;
+        tc_fence_after_sync();
+
+        // ---- y epilogue: round to bf16 into the (now free) A tile, one TMA store per chunk
+        {
+            uint32_t v32[32];
+            tmem_ld_16x256b_x8(tmY + wl, v32);
+            tmem_wait_ld();
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const int t0r = 16 * warp + r0, j = 8 * n + 2 * q;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r, j)) =
+                    pack_bf2(__uint_as_float(v32[4 * n]), __uint_as_float(v32[4 * n + 1]));
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r + 8, j)) =
+                    pack_bf2(__uint_as_float(v32[4 * n + 2]), __uint_as_float(v32[4 * n + 3]));
+            }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
+        if (tid == 0) {
+            tma_store_3d(&tm_y, sAM, h * 64, c * kChunk, b);
+            bulk_commit();
+            if (c + 2 < nchunks) { issue_loads(c + 2); ++loads_pending; }
+        }
+    }
+
+    // ---- unwind: drain this CTA's copies, report, release tensor memory
+    if (tid == 0) {
+        if (err != 0) {
+            // loads still in flight target this CTA's shared memory: wait for them (bounded) before leaving
+            for (int st = 0; st < 2 && loads_pending > 0; ++st) {
+                // parity unknown after an error: poll both
+                for (uint32_t it = 0; it < (1u << 16); ++it)
+                    if (mbar_try_wait(&bar_full[st], 0) || mbar_try_wait(&bar_full[st], 1)) break;
+            }
+            atomicExch(&g_chunk_status, err);
+        }
+        bulk_wait<0>();
+    }
+    if (err == 0 && a.s_out != nullptr) {
+        const size_t so = (size_t)blockIdx.x * 4096;
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = 16 * warp + r0 + (e >= 2 ? 8 : 0), j = 8 * n + 2 * q + (e & 1);
+                store_any(a.s_out, a.s_dtype, so + (size_t)i * 64 + j, S[4 * n + e]);
+            }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tb, 256);
+}
+
+}  // namespace wkv6

@@ -21,8 +21,18 @@ int cuda_fail(cudaError_t e, const char *what);
 size_t dtype_size(int dt);
 int validate(const wkv6_problem *p, Dims *d);
 
+// sequential variant (wkv6_seq.cu)
+int seq_forward(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v, const void *w,
+                const void *u, void *y, const void *s_in, const int64_t *s_map, int s_kinds, void *s_out,
+                cudaStream_t st);
+size_t seq_backward_workspace(const wkv6_problem *p, const Dims &d);
+int seq_backward(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v, const void *w,
+                 const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu, void *ws,
+                 size_t ws_bytes, cudaStream_t st);
+
 // chunked tensor-core variant (wkv6_chunk.cu)
 bool chunk_supported(const wkv6_problem *p);
+int chunk_status();
 size_t chunk_ckpt_bytes(const wkv6_problem *p);
 size_t chunk_backward_workspace(const wkv6_problem *p, const Dims &d, int have_ckpt);
 int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v, const void *w,

@@ -1,0 +1,105 @@
+"""GPU parity tests of the chunked tensor-core variant (bf16 inputs, fp32 state), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL_BF16, np_, oracle_all, rounded, scaled_err
+from oracle import c_oracle, wkv6_oracle as O
+
+pytestmark = pytest.mark.gpu
+N = 64
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    import star_rwkv6_b200 as m
+    return m
+
+
+def dev_inputs(d):
+    t = {n: torch.tensor(d[n]).to(torch.bfloat16).cuda() for n in ("r", "k", "v", "w", "gy")}
+    t["u"] = torch.tensor(d["u"]).cuda()
+    return t
+
+
+def status(pkg):
+    from star_rwkv6_b200 import _lib
+    return _lib.lib.wkv6_device_status()
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 64, 1), (2, 128, 2), (1, 256, 3), (2, 1000, 2), (1, 1, 1), (1, 65, 2), (3, 4096, 2)])
+def test_forward_vs_oracle(pkg, B, T, H):
+    d = O.make_inputs(B, T, H, N, seed=T + H)
+    t = dev_inputs(d)
+    y, s, _ = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_state=True, variant=pkg.VARIANT_CHUNK)
+    torch.cuda.synchronize()
+    assert status(pkg) == 0
+    dr = rounded(d, torch.bfloat16)
+    yo, so = c_oracle.fwd(dr["r"], dr["k"], dr["v"], dr["w"], dr["u"], N)
+    assert np.isfinite(np_(y)).all()
+    assert scaled_err(np_(y), yo) <= TOL_BF16
+    assert scaled_err(np_(s), so) <= TOL_BF16
+
+
+def test_forward_matches_sequential_kernel(pkg):
+    # the two variants see identical bf16 inputs; they differ only by operand rounding inside the chunked one
+    d = O.make_inputs(2, 512, 4, N, seed=21)
+    t = dev_inputs(d)
+    yc, sc, _ = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_state=True, variant=pkg.VARIANT_CHUNK)
+    ys, ss, _ = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_state=True, variant=pkg.VARIANT_SEQ)
+    assert scaled_err(np_(yc), np_(ys)) <= TOL_BF16
+    assert scaled_err(np_(sc), np_(ss)) <= 5e-3
+
+
+def test_state_in_and_map(pkg):
+    B, T, H = 3, 200, 2
+    d = O.make_inputs(B, T, H, N, seed=22, with_state=True, kinds=2)
+    t = dev_inputs(d)
+    s_in = torch.tensor(d["init_state"]).cuda()
+    smap = torch.tensor(d["state_map"]).cuda()
+    y, s, _ = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, s_in=s_in, s_map=smap, want_state=True,
+                              variant=pkg.VARIANT_CHUNK)
+    dr = rounded(d, torch.bfloat16)
+    yo, so = c_oracle.fwd(dr["r"], dr["k"], dr["v"], dr["w"], dr["u"], N, d["init_state"], d["state_map"])
+    assert scaled_err(np_(y), yo) <= TOL_BF16
+    assert scaled_err(np_(s), so) <= TOL_BF16
+
+
+def test_extreme_decay(pkg):
+    # w = -1e9 (masked steps: decay exactly 1) and w far above the benchmark range (decay clamped at e^-10)
+    B, T, H = 1, 192, 2
+    d = O.make_inputs(B, T, H, N, seed=23)
+    d["w"][:, 10:20] = -1e9
+    d["w"][:, 70:75] = 3.0
+    d["w"][:, 100] = 8.0
+    t = dev_inputs(d)
+    y, s, _ = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_state=True, variant=pkg.VARIANT_CHUNK)
+    dr = rounded(d, torch.bfloat16)
+    yo, so = c_oracle.fwd(dr["r"], dr["k"], dr["v"], dr["w"], dr["u"], N)
+    assert np.isfinite(np_(y)).all() and np.isfinite(np_(s)).all()
+    assert scaled_err(np_(y), yo) <= TOL_BF16
+    assert scaled_err(np_(s), so) <= TOL_BF16
+
+
+def test_bit_identical_reruns(pkg):
+    d = O.make_inputs(2, 320, 2, N, seed=24)
+    t = dev_inputs(d)
+    a = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_state=True, variant=pkg.VARIANT_CHUNK)
+    b = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_state=True, variant=pkg.VARIANT_CHUNK)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_operator_autograd_bf16(pkg):
+    from star_rwkv6_b200.rwkv_kernel.torch_rwkv_kernel import RWKVKernelOperator
+    d = O.make_inputs(2, 256, 2, N, seed=25)
+    op = RWKVKernelOperator(N, 256)  # AUTO -> chunked for bf16 / N=64
+    t = {n: torch.tensor(d[n]).to(torch.bfloat16).cuda().requires_grad_(True) for n in ("r", "k", "v", "w")}
+    u = torch.tensor(d["u"]).cuda().requires_grad_(True)
+    y, _ = op(t["r"], t["k"], t["v"], t["w"], u)
+    y.backward(torch.tensor(d["gy"]).to(torch.bfloat16).cuda())
+    ref = oracle_all(rounded(d, torch.bfloat16), N)
+    got = dict(y=np_(y), gr=np_(t["r"].grad), gk=np_(t["k"].grad), gv=np_(t["v"].grad), gw=np_(t["w"].grad),
+               gu=np_(u.grad))
+    for n in got:
+        assert scaled_err(got[n], ref[n]) <= TOL_BF16, n
+    assert status(pkg) == 0
