@@ -2,6 +2,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include "wkv6_chunk_bwd.cuh"
 #include "wkv6_chunk_fwd.cuh"
 #include "wkv6_internal.h"
 
@@ -52,10 +53,10 @@ int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const voi
     if ((rc = make_map(&mk, k, p, d, "k"))) return rc;
     if ((rc = make_map(&mv, v, p, d, "v"))) return rc;
     if ((rc = make_map(&mw, w, p, d, "w"))) return rc;
-    if ((rc = make_map(&my, y, p, d, "y"))) return rc;
+    if ((rc = make_map(&my, y ? y : r, p, d, "y"))) return rc;  // y == NULL: states only, the map is never used
     ChunkFwdArgs a{};
     a.u = u; a.u_dtype = p->u_dtype; a.s_in = s_in; a.s_map = s_map; a.s_kinds = s_kinds; a.s_dtype = p->s_dtype;
-    a.s_out = s_out; a.ckpt = static_cast<__nv_bfloat16 *>(ckpt); a.B = p->B; a.T = p->T; a.H = p->H;
+    a.s_out = s_out; a.write_y = (y != nullptr); a.ckpt = static_cast<__nv_bfloat16 *>(ckpt); a.B = p->B; a.T = p->T; a.H = p->H;
     cudaError_t e = cudaFuncSetAttribute(chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ChunkFwdSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_fwd_kernel)");
@@ -64,13 +65,42 @@ int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const voi
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_fwd_kernel launch");
 }
 
-// Until the chunked backward lands the gradients come from the sequential kernels.
-size_t chunk_backward_workspace(const wkv6_problem *p, const Dims &d, int) { return seq_backward_workspace(p, d); }
+// Without a checkpoint buffer from the forward, the backward first rebuilds the chunk-start states with the
+// forward kernel (its y output suppressed) inside the workspace.
+size_t chunk_backward_workspace(const wkv6_problem *p, const Dims &, int have_ckpt) {
+    return have_ckpt ? 0 : chunk_ckpt_bytes(p);
+}
 
 int chunk_backward(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v, const void *w,
-                   const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu, const void *,
+                   const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu, const void *ckpt,
                    void *ws, size_t ws_bytes, cudaStream_t st) {
-    return seq_backward(p, d, r, k, v, w, u, gy, gr, gk, gv, gw, gu, ws, ws_bytes, st);
+    int rc;
+    if (ckpt == nullptr) {
+        const size_t need = chunk_ckpt_bytes(p);
+        if (ws == nullptr || ws_bytes < need)
+            return fail(WKV6_ERR_WORKSPACE, "backward workspace: need %zu bytes, got %zu", need, ws ? ws_bytes : (size_t)0);
+        if ((rc = chunk_forward(p, d, r, k, v, w, u, nullptr, nullptr, nullptr, 0, nullptr, ws, st))) return rc;
+        ckpt = ws;
+    }
+    CUtensorMap mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw;
+    if ((rc = make_map(&mr, r, p, d, "r"))) return rc;
+    if ((rc = make_map(&mk, k, p, d, "k"))) return rc;
+    if ((rc = make_map(&mv, v, p, d, "v"))) return rc;
+    if ((rc = make_map(&mw, w, p, d, "w"))) return rc;
+    if ((rc = make_map(&mgy, gy, p, d, "gy"))) return rc;
+    if ((rc = make_map(&mgr, gr, p, d, "gr"))) return rc;
+    if ((rc = make_map(&mgk, gk, p, d, "gk"))) return rc;
+    if ((rc = make_map(&mgv, gv, p, d, "gv"))) return rc;
+    if ((rc = make_map(&mgw, gw, p, d, "gw"))) return rc;
+    ChunkBwdArgs a{};
+    a.u = u; a.u_dtype = p->u_dtype; a.gu = gu; a.gu_dtype = p->gu_dtype;
+    a.ckpt = static_cast<const __nv_bfloat16 *>(ckpt); a.B = p->B; a.T = p->T; a.H = p->H;
+    cudaError_t e = cudaFuncSetAttribute(chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ChunkBwdSmem::kAlloc);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_kernel)");
+    chunk_bwd_kernel<<<p->B * p->H, 256, ChunkBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_bwd_kernel launch");
 }
 
 int chunk_status() {

@@ -1,0 +1,635 @@
+// Chunked WKV6 backward for sm_100a.  One CTA walks the 64-token chunks of one (batch, head) sequence in
+// descending time; the reverse state Abar (N x N, fp32) and the running sum Z stay on chip across chunks, the
+// forward state at each chunk start comes from the bf16 checkpoints the forward wrote.
+//
+// With c_t the inclusive running sum of log-decays inside the chunk, P[t][s] = gy_t . v_s (s < t; the diagonal
+// vg_t = gy_t . v_t is kept aside), A the forward intra-chunk matrix (see wkv6_chunk_fwd.cuh):
+//   gr_t[i] = e^{c_{t-1}[i]} ( sum_{s<t} P[t][s] k_s[i] e^{-c_s[i]}  +  sum_j S_in[i][j] gy_t[j] )  + u_i k_t[i] vg_t
+//   gk_s[i] = e^{-c_s[i]}   ( sum_{t>s} P[t][s] r_t[i] e^{c_{t-1}[i]} + e^{c_63[i]} sum_j Abar[i][j] v_s[j] ) + u_i r_s[i] vg_s
+//   gv_s[j] = sum_{t>=s} A[t][s] gy_t[j] + sum_i k_s[i] e^{c_63[i]-c_s[i]} Abar[i][j]
+//   Abar'   = diag(e^{c_63}) Abar + sum_t (r_t e^{c_{t-1}}) (x) gy_t
+//   gw_t[i] = -exp(w_t[i]) G_t[i],   G_t = e^{c_63} <S_in, Abar>_i + sum_{tau>t} (r_tau e^{c_{tau-1}}) GR2[tau]
+//                                         + sum_{s<t} (k_s e^{c_63-c_s}) GK2[s] + sum_{s<t<tau} e^{c_{tau-1}-c_s} k_s r_tau P[tau][s]
+//   where GR2 = gy S_in^T and GK2 = v Abar^T.  The last (rectangle) sum is obtained as
+//   sum_{tau>t} r~_tau GR1[tau] - sum_{s>=t} k~_s GK1[s] from the intra-chunk parts GR1, GK1 of gr and gk: every product
+//   e^{..} k_s r_tau P[tau][s] with s, tau > t occurs in both sums and cancels, and it cancels exactly because (1) the
+//   block reference points are rounded to integers in the log2 domain, so the block-pair factor is a power of two
+//   and commutes with bf16 rounding, and (2) the multipliers r~, k~ used here are the bf16-rounded operand values.
+// The exponentials are split around per-16-token-block reference points exactly as in the forward, so every
+// bf16 operand stays finite; block pairs (I, J) are separate MMAs whose output is restricted to the 16 rows of
+// one block with the disable-output-lane mask of tcgen05.mma.
+//
+// All element-wise work is done in the accumulator-fragment layout of tcgen05.ld.16x256b: a thread owns tokens
+// {r0, r0+8} of block (warp & 3) and channels 8n+2q, 8n+2q+1 for four values of n ((warp >> 2) selects which
+// four), so the per-element decay factors computed before the MMAs are still in registers when the
+// accumulators come back.  Running sums along time are lane scans over the 8 lanes that share q.
+//
+// Tensor-memory map (256 columns): lanes 0-15: [0,64) P -> GR1 | [64,128) A -> GK1 | [128,192) GR2 | [192,256) GK2
+//                                  lanes 16-31: [0,64) Abar increment | [64,128) gv
+#pragma once
+
+#include "wkv6_chunk_fwd.cuh"
+
+namespace wkv6 {
+
+struct ChunkBwdSmem {
+    static constexpr int oR = 0;                    // r  -> r~ (in place)
+    static constexpr int oK = oR + kTile;           // k  -> k~ (in place)
+    static constexpr int oV = oK + kTile;
+    static constexpr int oW = oV + kTile;           // w  -> r^ = r~ e^{c_rho - c_start} (in place)
+    static constexpr int oG = oW + kTile;           // gy
+    static constexpr int oS = oG + kTile;           // checkpointed state at the chunk start [i][j]
+    static constexpr int oKH = oS + kTile;          // k^ = k~ e^{c_63 - c_rho}
+    static constexpr int oKD = oKH + kTile;         // k~ copies for block distances 1..3 (96 rows); later the gv tile
+    static constexpr int oRD = oKD + 96 * 128;      // r~ copies for block distances 1..3 (96 rows); later the gw tile
+    static constexpr int oP = oRD + 96 * 128;       // masked P (bf16); later the gr tile
+    static constexpr int oAM = oP + kTile;          // masked A (bf16); later the gk tile
+    static constexpr int oAB = oAM + kTile;         // bf16 copy of Abar [i][j]
+    static constexpr int oHead = oAB + kTile;       // float [4][64] log2-decay sum of the first 8 tokens of a block
+    static constexpr int oTot = oHead + 1024;       // float [4][64] log2-decay sum of the block
+    static constexpr int oRef = oTot + 1024;        // float [4][64] integer reference point of the block (chunk-relative, log2)
+    static constexpr int oOff = oRef + 1024;        // float [4][64] reference point relative to the block start
+    static constexpr int oFK = oOff + 1024;         // float [4][64] 2^{c_63 - ref(J)}
+    static constexpr int oDtot = oFK + 1024;        // float [64]    2^{c_63}
+    static constexpr int oBonus = oDtot + 256;      // float [2][64]
+    static constexpr int oVG = oBonus + 512;        // float [64]
+    static constexpr int oT1 = oVG + 256;           // float [64]    <S_in, Abar>_i
+    static constexpr int oXtot = oTot;              // float [4][64] block sums for gw (sTot is dead by then)
+    static constexpr int oBtot = oHead;             // float [4][64] block sums for gw (sHead is dead by then)
+    static constexpr int oGU = oHead;               // float [4][64] final reduction of gu (after the last chunk)
+    static constexpr int oBar = oT1 + 256;          // full, mma1, mma2
+    static constexpr int oSlot = oBar + 32;
+    static constexpr int kBytes = oSlot + 16;
+    static constexpr int kAlloc = kBytes + 1008;  // the dynamic base is 16-byte aligned; the tiles need 1024
+};
+
+struct ChunkBwdArgs {
+    const void *u; int u_dtype;
+    void *gu; int gu_dtype;
+    const __nv_bfloat16 *ckpt;
+    int B, T, H;
+};
+
+// D[tmem] (+)= A * B restricted to the TMEM lanes whose mask bit is 0.
+__device__ __forceinline__ void umma_ss_masked(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               bool accumulate, int enabled_block) {
+    const uint32_t on = 0xFFFF0000u, off = 0xFFFFFFFFu;
+    const uint32_t m0 = enabled_block == 0 ? on : off, m1 = enabled_block == 1 ? on : off;
+    const uint32_t m2 = enabled_block == 2 ? on : off, m3 = enabled_block == 3 ? on : off;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)accumulate), "r"(m0), "r"(m1), "r"(m2), "r"(m3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, float (&f)[16]) {
+    uint32_t v[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
+}
+
+// 2^n for an integer-valued float n (exact; flushes to zero below the normal range)
+__device__ __forceinline__ float pow2i(float n) {
+    const int e = (int)n + 127;
+    return e <= 0 ? 0.f : __int_as_float((e > 254 ? 254 : e) << 23);
+}
+
+// inclusive prefix over the 16 tokens of a block: a = row r0, b = row r0 + 8, lanes sharing q hold consecutive r0
+__device__ __forceinline__ void scan_prefix16(float &a, float &b, int r0, int lane) {
+#pragma unroll
+    for (int d = 1; d < 8; d <<= 1) {
+        const float ta = __shfl_up_sync(0xffffffffu, a, 4 * d);
+        const float tb = __shfl_up_sync(0xffffffffu, b, 4 * d);
+        if (r0 >= d) { a += ta; b += tb; }
+    }
+    b += __shfl_sync(0xffffffffu, a, 28 + (lane & 3));
+}
+// inclusive suffix over the 16 tokens of a block
+__device__ __forceinline__ void scan_suffix16(float &a, float &b, int r0, int lane) {
+#pragma unroll
+    for (int d = 1; d < 8; d <<= 1) {
+        const float ta = __shfl_down_sync(0xffffffffu, a, 4 * d);
+        const float tb = __shfl_down_sync(0xffffffffu, b, 4 * d);
+        if (r0 + d < 8) { a += ta; b += tb; }
+    }
+    a += __shfl_sync(0xffffffffu, b, lane & 3);
+}
+
+__global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant__ CUtensorMap tm_r,
+                                                           const __grid_constant__ CUtensorMap tm_k,
+                                                           const __grid_constant__ CUtensorMap tm_v,
+                                                           const __grid_constant__ CUtensorMap tm_w,
+                                                           const __grid_constant__ CUtensorMap tm_gy,
+                                                           const __grid_constant__ CUtensorMap tm_gr,
+                                                           const __grid_constant__ CUtensorMap tm_gk,
+                                                           const __grid_constant__ CUtensorMap tm_gv,
+                                                           const __grid_constant__ CUtensorMap tm_gw,
+                                                           const ChunkBwdArgs a) {
+    using namespace ptx;
+    using SM = ChunkBwdSmem;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *sR = smem + SM::oR, *sK = smem + SM::oK, *sV = smem + SM::oV, *sW = smem + SM::oW, *sG = smem + SM::oG;
+    uint8_t *sS = smem + SM::oS, *sKH = smem + SM::oKH, *sKD = smem + SM::oKD, *sRD = smem + SM::oRD;
+    uint8_t *sP = smem + SM::oP, *sAM = smem + SM::oAM, *sAB = smem + SM::oAB;
+    float *sHead = reinterpret_cast<float *>(smem + SM::oHead), *sTot = reinterpret_cast<float *>(smem + SM::oTot);
+    float *sRef = reinterpret_cast<float *>(smem + SM::oRef), *sOff = reinterpret_cast<float *>(smem + SM::oOff);
+    float *sFK = reinterpret_cast<float *>(smem + SM::oFK), *sDtot = reinterpret_cast<float *>(smem + SM::oDtot);
+    float *sBonus = reinterpret_cast<float *>(smem + SM::oBonus), *sVG = reinterpret_cast<float *>(smem + SM::oVG);
+    float *sXtot = reinterpret_cast<float *>(smem + SM::oXtot), *sBtot = reinterpret_cast<float *>(smem + SM::oBtot);
+    float *sT1 = reinterpret_cast<float *>(smem + SM::oT1);
+    float *sGU = reinterpret_cast<float *>(smem + SM::oGU);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SM::oBar);
+    uint64_t *bar_full = bars, *bar_mma1 = bars + 1, *bar_mma2 = bars + 2;
+    uint32_t *slot = reinterpret_cast<uint32_t *>(smem + SM::oSlot);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int w4 = warp & 3, half = warp >> 2, n0 = 4 * half;
+    const int r0 = lane >> 2, q = lane & 3;
+    const int ta = 16 * w4 + r0;  // this thread's rows: ta and ta + 8
+    const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
+    const int nchunks = (a.T + kChunk - 1) / kChunk;
+
+    if (tid == 0) {
+        mbar_init(bar_full, 1);
+        mbar_init(bar_mma1, 1);
+        mbar_init(bar_mma2, 1);
+        fence_mbar_init();
+        prefetch_tensormap(&tm_r); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_w);
+        prefetch_tensormap(&tm_gy); prefetch_tensormap(&tm_gr); prefetch_tensormap(&tm_gk);
+        prefetch_tensormap(&tm_gv); prefetch_tensormap(&tm_gw);
+    }
+    if (warp == 0) {
+        tmem_alloc(slot, 256);
+        tmem_relinquish();
+    }
+    // zero: the reverse state (registers + operand copy), Z, and the copy tiles whose unused rows are never written
+    float AB[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) AB[e] = 0.f;
+    for (int o = tid * 16; o < kTile; o += 256 * 16) *reinterpret_cast<uint4 *>(sAB + o) = make_uint4(0, 0, 0, 0);
+    float gu_acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) gu_acc[e] = 0.f;
+    float u_c[8];  // u of this thread's channels
+#pragma unroll
+    for (int nn = 0; nn < 4; ++nn) {
+        u_c[2 * nn] = load_any(a.u, a.u_dtype, (size_t)h * 64 + 8 * (n0 + nn) + 2 * q);
+        u_c[2 * nn + 1] = load_any(a.u, a.u_dtype, (size_t)h * 64 + 8 * (n0 + nn) + 2 * q + 1);
+    }
+
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tbase = *slot;
+    const uint32_t lo = (uint32_t)(32 * w4) << 16;  // this warp's TMEM lane quarter
+    const uint32_t tmP = tbase, tmA = tbase + 64, tmGR2 = tbase + 128, tmGK2 = tbase + 192;
+    const uint32_t tmAN = tbase + (16u << 16), tmGV = tbase + (16u << 16) + 64;
+    const uint32_t cb = 8 * n0;  // first accumulator column of this thread's fragment
+
+    auto issue_loads = [&](int c) {
+        mbar_expect_tx(bar_full, 6 * kTile);
+        tma_load_3d(sR, &tm_r, bar_full, h * 64, c * kChunk, b);
+        tma_load_3d(sK, &tm_k, bar_full, h * 64, c * kChunk, b);
+        tma_load_3d(sV, &tm_v, bar_full, h * 64, c * kChunk, b);
+        tma_load_3d(sW, &tm_w, bar_full, h * 64, c * kChunk, b);
+        tma_load_3d(sG, &tm_gy, bar_full, h * 64, c * kChunk, b);
+        bulk_load(sS, a.ckpt + ((size_t)blockIdx.x * nchunks + c) * 4096, kTile, bar_full);
+    };
+    if (tid == 0) issue_loads(nchunks - 1);
+
+    constexpr uint32_t idKK = umma_idesc_bf16(64, 64, false, false);
+    constexpr uint32_t idKK16 = umma_idesc_bf16(64, 16, false, false);
+    constexpr uint32_t idKM = umma_idesc_bf16(64, 64, false, true);
+    constexpr uint32_t idMM = umma_idesc_bf16(64, 64, true, true);
+    const int goff[4] = {0, 0, 48, 80};  // first row of the distance-d copies inside sKD / sRD
+
+    int err = 0;
+    bool load_pending = true;  // thread 0
+    for (int it = 0; it < nchunks; ++it) {
+        const int c = nchunks - 1 - it;
+        if (!mbar_wait(bar_full, it & 1)) err = 1;
+        if (tid == 0) load_pending = false;
+
+        // ---- per-step log2 decays and their running sums inside the block (fragment layout)
+        uint32_t rp[8], kp[8];  // raw r, k as packed bf16 pairs: index 2*nn + (0: row ta, 1: row ta+8)
+        float cs[16], lw[16];
+#pragma unroll
+        for (int nn = 0; nn < 4; ++nn) {
+            const int col = 8 * (n0 + nn) + 2 * q;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int t = ta + 8 * hrow;
+                const uint32_t off = sw128_off(t, col);
+                rp[2 * nn + hrow] = *reinterpret_cast<const uint32_t *>(sR + off);
+                kp[2 * nn + hrow] = *reinterpret_cast<const uint32_t *>(sK + off);
+                const float2 w2 = ld_bf2(sW + off);
+                float lx = fmaxf(-ex2f(w2.x * kLog2e) * kLog2e, kMinLogDecay2);
+                float ly = fmaxf(-ex2f(w2.y * kLog2e) * kLog2e, kMinLogDecay2);
+                if (c * kChunk + t >= a.T) { lx = 0.f; ly = 0.f; }
+                lw[4 * nn + 2 * hrow] = lx;
+                lw[4 * nn + 2 * hrow + 1] = ly;
+            }
+        }
+#pragma unroll
+        for (int nn = 0; nn < 4; ++nn)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float pa = lw[4 * nn + e], pb = lw[4 * nn + 2 + e];
+                scan_prefix16(pa, pb, r0, lane);
+                cs[4 * nn + e] = pa;
+                cs[4 * nn + 2 + e] = pb;
+            }
+        if (r0 == 7) {
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int col = 8 * (n0 + nn) + 2 * q;
+                *reinterpret_cast<float2 *>(&sHead[w4 * 64 + col]) = make_float2(cs[4 * nn], cs[4 * nn + 1]);
+                *reinterpret_cast<float2 *>(&sTot[w4 * 64 + col]) = make_float2(cs[4 * nn + 2], cs[4 * nn + 3]);
+            }
+        }
+        if (tid < 64) sT1[tid] = 0.f;  // accumulated in epilogue 1
+        if (tid == 0) bulk_wait_read<0>();  // the previous chunk's output tiles have left shared memory
+        if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
+
+        // ---- per (block, channel) factors, one pair per thread
+        {
+            const int J = tid >> 6, i = tid & 63;
+            float base = 0.f, mybase = 0.f, myref = 0.f, all = 0.f;
+#pragma unroll
+            for (int J2 = 0; J2 < 4; ++J2) {
+                const float rf = rintf(base + sHead[J2 * 64 + i]);  // integer: block-pair factors become powers of two
+                if (J2 == J) { mybase = base; myref = rf; }
+                base += sTot[J2 * 64 + i];
+            }
+            all = base;
+            sRef[J * 64 + i] = myref;
+            sOff[J * 64 + i] = myref - mybase;
+            sFK[J * 64 + i] = ex2f(all - myref);
+            if (J == 0) sDtot[i] = ex2f(all);
+        }
+        __syncthreads();
+
+        // ---- scaled operands
+        {
+            float bon_a = 0.f, bon_b = 0.f;
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int col = 8 * (n0 + nn) + 2 * q;
+                const float2 of = *reinterpret_cast<const float2 *>(&sOff[w4 * 64 + col]);
+                const float2 rf = *reinterpret_cast<const float2 *>(&sRef[w4 * 64 + col]);
+                const float2 fk = *reinterpret_cast<const float2 *>(&sFK[w4 * 64 + col]);
+                const float2 fr = make_float2(pow2i(rf.x), pow2i(rf.y));
+                float2 mk[3], mr[3];  // power-of-two factors of the copies for block distances 1..3
+#pragma unroll
+                for (int d = 1; d <= 3; ++d) {
+                    mk[d - 1] = mr[d - 1] = make_float2(0.f, 0.f);
+                    if (w4 + d <= 3) {
+                        const float2 rt2 = *reinterpret_cast<const float2 *>(&sRef[(w4 + d) * 64 + col]);
+                        mk[d - 1] = make_float2(pow2i(rt2.x - rf.x), pow2i(rt2.y - rf.y));
+                    }
+                    if (w4 - d >= 0) {
+                        const float2 rs2 = *reinterpret_cast<const float2 *>(&sRef[(w4 - d) * 64 + col]);
+                        mr[d - 1] = make_float2(pow2i(rf.x - rs2.x), pow2i(rf.y - rs2.y));
+                    }
+                }
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    const int t = ta + 8 * hrow;
+                    const uint32_t off = sw128_off(t, col);
+                    const int e0 = 4 * nn + 2 * hrow;
+                    const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&rp[2 * nn + hrow]));
+                    const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kp[2 * nn + hrow]));
+                    const float erx = ex2f(cs[e0] - lw[e0] - of.x), ery = ex2f(cs[e0 + 1] - lw[e0 + 1] - of.y);
+                    const float ekx = ex2f(of.x - cs[e0]), eky = ex2f(of.y - cs[e0 + 1]);
+                    const float rtx = __fmul_rn(r2.x, erx), rty = __fmul_rn(r2.y, ery);
+                    const float ktx = __fmul_rn(k2.x, ekx), kty = __fmul_rn(k2.y, eky);
+                    const float bon = r2.x * u_c[2 * nn] * k2.x + r2.y * u_c[2 * nn + 1] * k2.y;
+                    if (hrow == 0) bon_a += bon; else bon_b += bon;
+                    st_bf2(sR + off, rtx, rty);
+                    st_bf2(sW + off, rtx * fr.x, rty * fr.y);
+                    st_bf2(sK + off, ktx, kty);
+                    st_bf2(sKH + off, ktx * fk.x, kty * fk.y);
+#pragma unroll
+                    for (int d = 1; d <= 3; ++d) {
+                        if (w4 + d <= 3)  // k~ copy serving row block w4 + d
+                            st_bf2(sKD + sw128_off(goff[d] + t, col), ktx * mk[d - 1].x, kty * mk[d - 1].y);
+                        if (w4 - d >= 0)  // r~ copy serving column block w4 - d
+                            st_bf2(sRD + sw128_off(goff[d] + t - 16 * d, col), rtx * mr[d - 1].x, rty * mr[d - 1].y);
+                    }
+                }
+            }
+            bon_a += __shfl_xor_sync(0xffffffffu, bon_a, 1); bon_a += __shfl_xor_sync(0xffffffffu, bon_a, 2);
+            bon_b += __shfl_xor_sync(0xffffffffu, bon_b, 1); bon_b += __shfl_xor_sync(0xffffffffu, bon_b, 2);
+            if (q == 0) { sBonus[half * 64 + ta] = bon_a; sBonus[half * 64 + ta + 8] = bon_b; }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncthreads();
+
+        // ---- MMA group 1
+        if (tid == 0) {
+            tc_fence_after_sync();
+            const uint32_t aR = smem_u32(sR), aK = smem_u32(sK), aV = smem_u32(sV), aW = smem_u32(sW), aG = smem_u32(sG);
+            const uint32_t aS = smem_u32(sS), aKH = smem_u32(sKH), aKD = smem_u32(sKD), aAB = smem_u32(sAB);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // P = gy v^T
+                umma_ss(tmP, umma_desc_sw128(aG + 32 * kk), umma_desc_sw128(aV + 32 * kk), idKK, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // A, distance-0 copies everywhere (valid on the diagonal blocks)
+                umma_ss(tmA, umma_desc_sw128(aR + 32 * kk), umma_desc_sw128(aK + 32 * kk), idKK, kk > 0);
+#pragma unroll
+            for (int I = 1; I < 4; ++I)
+#pragma unroll
+                for (int J = 0; J < I; ++J)  // A block (I, J) from the distance-(I-J) copy of k~_J
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_ss_masked(tmA + 16 * J, umma_desc_sw128(aR + 32 * kk),
+                                       umma_desc_sw128(aKD + (goff[I - J] + 16 * J) * 128 + 32 * kk), idKK16, kk > 0, I);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // GR2 = gy S_in^T
+                umma_ss(tmGR2, umma_desc_sw128(aG + 32 * kk), umma_desc_sw128(aS + 32 * kk), idKK, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // GK2 = v Abar^T
+                umma_ss(tmGK2, umma_desc_sw128(aV + 32 * kk), umma_desc_sw128(aAB + 32 * kk), idKK, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // Abar increment = r^^T gy
+                umma_ss(tmAN, umma_desc_sw128(aW + 2048 * kk), umma_desc_sw128(aG + 2048 * kk), idMM, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // gv = k^ Abar
+                umma_ss(tmGV, umma_desc_sw128(aKH + 32 * kk), umma_desc_sw128(aAB + 2048 * kk), idKM, kk > 0);
+            umma_commit(bar_mma1);
+        }
+        if (!mbar_wait(bar_mma1, it & 1)) err = 2;
+        tc_fence_after_sync();
+
+        // ---- epilogue 1: masked P and A as bf16 operands, reverse-state update
+        {
+            float f[16];
+            tmem_ld_16x256b_x4(tmP + lo + cb, f);
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int s0 = 8 * (n0 + nn) + 2 * q;  // columns s0, s0 + 1
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    const int t = ta + 8 * hrow;
+                    float x0 = f[4 * nn + 2 * hrow], x1 = f[4 * nn + 2 * hrow + 1];
+                    if (s0 == t) sVG[t] = x0;
+                    if (s0 + 1 == t) sVG[t] = x1;
+                    x0 = (s0 < t) ? x0 : 0.f;
+                    x1 = (s0 + 1 < t) ? x1 : 0.f;
+                    *reinterpret_cast<uint32_t *>(sP + sw128_off(t, s0)) = pack_bf2(x0, x1);
+                }
+            }
+            tmem_ld_16x256b_x4(tmA + lo + cb, f);
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int s0 = 8 * (n0 + nn) + 2 * q;
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    const int t = ta + 8 * hrow;
+                    float x0 = f[4 * nn + 2 * hrow], x1 = f[4 * nn + 2 * hrow + 1];
+                    const float bonus = sBonus[t] + sBonus[64 + t];
+                    x0 = (s0 < t) ? x0 : (s0 == t ? bonus : 0.f);
+                    x1 = (s0 + 1 < t) ? x1 : (s0 + 1 == t ? bonus : 0.f);
+                    *reinterpret_cast<uint32_t *>(sAM + sw128_off(t, s0)) = pack_bf2(x0, x1);
+                }
+            }
+            // <S_in, Abar>_i with the reverse state at the chunk end (before its update), for gw
+            float za = 0.f, zb = 0.f;
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int j0 = 8 * (n0 + nn) + 2 * q;
+                const float2 sa = ld_bf2(sS + sw128_off(ta, j0)), sb = ld_bf2(sS + sw128_off(ta + 8, j0));
+                za = fmaf(AB[4 * nn], sa.x, fmaf(AB[4 * nn + 1], sa.y, za));
+                zb = fmaf(AB[4 * nn + 2], sb.x, fmaf(AB[4 * nn + 3], sb.y, zb));
+            }
+            za += __shfl_xor_sync(0xffffffffu, za, 1); za += __shfl_xor_sync(0xffffffffu, za, 2);
+            zb += __shfl_xor_sync(0xffffffffu, zb, 1); zb += __shfl_xor_sync(0xffffffffu, zb, 2);
+            if (q == 0) {  // two contributions per slot (the two column halves): the sum is order-independent
+                atomicAdd(&sT1[ta], za);
+                atomicAdd(&sT1[ta + 8], zb);
+            }
+            tmem_ld_16x256b_x4(tmAN + lo + cb, f);  // rows are key channels here
+            const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int j0 = 8 * (n0 + nn) + 2 * q;
+                AB[4 * nn + 0] = fmaf(AB[4 * nn + 0], d0, f[4 * nn + 0]);
+                AB[4 * nn + 1] = fmaf(AB[4 * nn + 1], d0, f[4 * nn + 1]);
+                AB[4 * nn + 2] = fmaf(AB[4 * nn + 2], d1, f[4 * nn + 2]);
+                AB[4 * nn + 3] = fmaf(AB[4 * nn + 3], d1, f[4 * nn + 3]);
+                *reinterpret_cast<uint32_t *>(sAB + sw128_off(ta, j0)) = pack_bf2(AB[4 * nn], AB[4 * nn + 1]);
+                *reinterpret_cast<uint32_t *>(sAB + sw128_off(ta + 8, j0)) = pack_bf2(AB[4 * nn + 2], AB[4 * nn + 3]);
+            }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        if (!__syncthreads_and(err == 0)) { err = err ? err : 11; break; }
+
+        // ---- MMA group 2
+        if (tid == 0) {
+            tc_fence_after_sync();
+            const uint32_t aR = smem_u32(sR), aK = smem_u32(sK), aG = smem_u32(sG), aP = smem_u32(sP);
+            const uint32_t aKD = smem_u32(sKD), aRD = smem_u32(sRD), aAM = smem_u32(sAM);
+#pragma unroll
+            for (int I = 0; I < 4; ++I)
+#pragma unroll
+                for (int J = 0; J <= I; ++J) {
+                    // GR1 rows of block I += P[:, block J] k~copy(I-J)_J        (K = the 16 tokens of block J)
+                    const uint32_t kb = (I == J) ? aK + 2048 * J : aKD + (goff[I - J] + 16 * J) * 128;
+                    umma_ss_masked(tmP, umma_desc_sw128(aP + 32 * J), umma_desc_sw128(kb), idKM, J > 0, I);
+                }
+#pragma unroll
+            for (int J = 0; J < 4; ++J)
+#pragma unroll
+                for (int I = J; I < 4; ++I) {
+                    // GK1 rows of block J += P[block I, :]^T r~copy(I-J)_I      (K = the 16 tokens of block I)
+                    const uint32_t rb = (I == J) ? aR + 2048 * I : aRD + (goff[I - J] + 16 * J) * 128;
+                    umma_ss_masked(tmA, umma_desc_sw128(aP + 2048 * I), umma_desc_sw128(rb), idMM, I > J, J);
+                }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // gv += A^T gy
+                umma_ss(tmGV, umma_desc_sw128(aAM + 2048 * kk), umma_desc_sw128(aG + 2048 * kk), idMM, true);
+            umma_commit(bar_mma2);
+        }
+        if (!mbar_wait(bar_mma2, it & 1)) err = 3;
+        tc_fence_after_sync();
+        // every input tile is dead once the second MMA group has completed: fetch the next chunk now
+        if (tid == 0 && c > 0 && err == 0) { issue_loads(c - 1); load_pending = true; }
+
+        // ---- epilogue 2: gr, gk, gv, gw
+        {
+            float g1[16], g2[16];
+            float qv[16], zb[16];  // qv = a - z - b (see the gw formula above), zb = z + b
+            const float vga = sVG[ta], vgb = sVG[ta + 8];
+            tmem_ld_16x256b_x4(tmP + lo + cb, g1);    // GR1
+            tmem_ld_16x256b_x4(tmGR2 + lo + cb, g2);  // GR2
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int col = 8 * (n0 + nn) + 2 * q;
+                const float2 of = *reinterpret_cast<const float2 *>(&sOff[w4 * 64 + col]);
+                const float2 rf = *reinterpret_cast<const float2 *>(&sRef[w4 * 64 + col]);
+                const float2 fr = make_float2(pow2i(rf.x), pow2i(rf.y));
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    const int e0 = 4 * nn + 2 * hrow;
+                    const float vg = hrow ? vgb : vga;
+                    const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&rp[2 * nn + hrow]));
+                    const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kp[2 * nn + hrow]));
+                    const float erx = ex2f(cs[e0] - lw[e0] - of.x), ery = ex2f(cs[e0 + 1] - lw[e0 + 1] - of.y);
+                    const float rtx = __fmul_rn(r2.x, erx), rty = __fmul_rn(r2.y, ery);  // as in the operand pass
+                    const float rbx = __bfloat162float(__float2bfloat16_rn(rtx)), rby = __bfloat162float(__float2bfloat16_rn(rty));
+                    const float grx = fmaf(erx, fmaf(fr.x, g2[e0], g1[e0]), u_c[2 * nn] * k2.x * vg);
+                    const float gry = fmaf(ery, fmaf(fr.y, g2[e0 + 1], g1[e0 + 1]), u_c[2 * nn + 1] * k2.y * vg);
+                    qv[e0] = fmaf(rbx, g1[e0], (rtx * fr.x) * g2[e0]);
+                    qv[e0 + 1] = fmaf(rby, g1[e0 + 1], (rty * fr.y) * g2[e0 + 1]);
+                    *reinterpret_cast<uint32_t *>(sP + sw128_off(ta + 8 * hrow, col)) = pack_bf2(grx, gry);
+                }
+            }
+            tmem_ld_16x256b_x4(tmA + lo + cb, g1);    // GK1
+            tmem_ld_16x256b_x4(tmGK2 + lo + cb, g2);  // GK2
+            float bsum[8];
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int col = 8 * (n0 + nn) + 2 * q;
+                const float2 of = *reinterpret_cast<const float2 *>(&sOff[w4 * 64 + col]);
+                const float2 fk = *reinterpret_cast<const float2 *>(&sFK[w4 * 64 + col]);
+                bsum[2 * nn] = 0.f; bsum[2 * nn + 1] = 0.f;
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    const int e0 = 4 * nn + 2 * hrow;
+                    const float vg = hrow ? vgb : vga;
+                    const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&rp[2 * nn + hrow]));
+                    const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kp[2 * nn + hrow]));
+                    const float ekx = ex2f(of.x - cs[e0]), eky = ex2f(of.y - cs[e0 + 1]);
+                    const float ktx = __fmul_rn(k2.x, ekx), kty = __fmul_rn(k2.y, eky);
+                    const float kbx = __bfloat162float(__float2bfloat16_rn(ktx)), kby = __bfloat162float(__float2bfloat16_rn(kty));
+                    const float gkx = fmaf(ekx, fmaf(fk.x, g2[e0], g1[e0]), u_c[2 * nn] * r2.x * vg);
+                    const float gky = fmaf(eky, fmaf(fk.y, g2[e0 + 1], g1[e0 + 1]), u_c[2 * nn + 1] * r2.y * vg);
+                    const float zx = kbx * g1[e0], zy = kby * g1[e0 + 1];
+                    const float bx = (ktx * fk.x) * g2[e0], by = (kty * fk.y) * g2[e0 + 1];
+                    zb[e0] = zx + bx; zb[e0 + 1] = zy + by;
+                    qv[e0] -= zb[e0]; qv[e0 + 1] -= zb[e0 + 1];
+                    bsum[2 * nn] += bx; bsum[2 * nn + 1] += by;
+                    gu_acc[2 * nn] = fmaf(r2.x * k2.x, vg, gu_acc[2 * nn]);
+                    gu_acc[2 * nn + 1] = fmaf(r2.y * k2.y, vg, gu_acc[2 * nn + 1]);
+                    *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta + 8 * hrow, col)) = pack_bf2(gkx, gky);
+                }
+            }
+            tmem_ld_16x256b_x4(tmGV + lo + cb, g1);
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int col = 8 * (n0 + nn) + 2 * q;
+                *reinterpret_cast<uint32_t *>(sKD + sw128_off(ta, col)) = pack_bf2(g1[4 * nn], g1[4 * nn + 1]);
+                *reinterpret_cast<uint32_t *>(sKD + sw128_off(ta + 8, col)) = pack_bf2(g1[4 * nn + 2], g1[4 * nn + 3]);
+            }
+            // sums over later tokens: inside the block by lane scans, across blocks through shared memory
+            float incl[16];
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float pa = qv[4 * nn + e], pb = qv[4 * nn + 2 + e];
+                    scan_suffix16(pa, pb, r0, lane);
+                    incl[4 * nn + e] = pa;
+                    incl[4 * nn + 2 + e] = pb;
+                    float bs = bsum[2 * nn + e];
+                    bs += __shfl_xor_sync(0xffffffffu, bs, 4);
+                    bs += __shfl_xor_sync(0xffffffffu, bs, 8);
+                    bs += __shfl_xor_sync(0xffffffffu, bs, 16);
+                    bsum[2 * nn + e] = bs;
+                }
+            if (r0 == 0) {
+#pragma unroll
+                for (int nn = 0; nn < 4; ++nn) {
+                    const int col = 8 * (n0 + nn) + 2 * q;
+                    *reinterpret_cast<float2 *>(&sXtot[w4 * 64 + col]) = make_float2(incl[4 * nn], incl[4 * nn + 1]);
+                    *reinterpret_cast<float2 *>(&sBtot[w4 * 64 + col]) = make_float2(bsum[2 * nn], bsum[2 * nn + 1]);
+                }
+            }
+            tc_fence_before_sync();
+            __syncthreads();
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int col = 8 * (n0 + nn) + 2 * q;
+                const float2 t1 = *reinterpret_cast<const float2 *>(&sT1[col]);
+                const float2 dt = *reinterpret_cast<const float2 *>(&sDtot[col]);
+                float2 base = make_float2(t1.x * dt.x, t1.y * dt.y);
+#pragma unroll
+                for (int J2 = 0; J2 < 4; ++J2) {
+                    const float2 bt = *reinterpret_cast<const float2 *>(&sBtot[J2 * 64 + col]);
+                    base.x += bt.x; base.y += bt.y;
+                    if (J2 > w4) {
+                        const float2 xt = *reinterpret_cast<const float2 *>(&sXtot[J2 * 64 + col]);
+                        base.x += xt.x; base.y += xt.y;
+                    }
+                }
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    const int e0 = 4 * nn + 2 * hrow;
+                    const int t = ta + 8 * hrow;
+                    const float gx = base.x + (incl[e0] - qv[e0]) - zb[e0];
+                    const float gy2 = base.y + (incl[e0 + 1] - qv[e0 + 1]) - zb[e0 + 1];
+                    float gwx = (lw[e0] * (1.0f / kLog2e)) * gx;  // -exp(w) = log-decay
+                    float gwy = (lw[e0 + 1] * (1.0f / kLog2e)) * gy2;
+                    if (c == 0 && t == 0) { gwx = 0.f; gwy = 0.f; }  // zero initial state: exactly no dependence on w_0
+                    *reinterpret_cast<uint32_t *>(sRD + sw128_off(t, col)) = pack_bf2(gwx, gwy);
+                }
+            }
+        }
+        fence_proxy_async_smem();
+        if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
+        if (tid == 0) {
+            tma_store_3d(&tm_gr, sP, h * 64, c * kChunk, b);
+            tma_store_3d(&tm_gk, sAM, h * 64, c * kChunk, b);
+            tma_store_3d(&tm_gv, sKD, h * 64, c * kChunk, b);
+            tma_store_3d(&tm_gw, sRD, h * 64, c * kChunk, b);
+            bulk_commit();
+        }
+    }
+
+    // ---- unwind
+    if (tid == 0) {
+        if (err != 0) {
+            if (load_pending)
+                for (uint32_t k2 = 0; k2 < (1u << 16); ++k2)
+                    if (mbar_try_wait(bar_full, 0) || mbar_try_wait(bar_full, 1)) break;
+            atomicExch(&g_chunk_status, 100 + err);
+        }
+        bulk_wait<0>();
+    }
+    // gu[b][h][i]: sum this thread's channels over the 8 lanes sharing q, then over the four row blocks
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        float s = gu_acc[e];
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 8);
+        s += __shfl_xor_sync(0xffffffffu, s, 16);
+        gu_acc[e] = s;
+    }
+    __syncthreads();
+    if (r0 == 0) {
+#pragma unroll
+        for (int nn = 0; nn < 4; ++nn) {
+            sGU[w4 * 64 + 8 * (n0 + nn) + 2 * q] = gu_acc[2 * nn];
+            sGU[w4 * 64 + 8 * (n0 + nn) + 2 * q + 1] = gu_acc[2 * nn + 1];
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid < 64 && err == 0)
+        store_any(a.gu, a.gu_dtype, (size_t)blockIdx.x * 64 + tid, sGU[tid] + sGU[64 + tid] + sGU[128 + tid] + sGU[192 + tid]);
+    if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+}  // namespace wkv6

@@ -58,6 +58,7 @@ struct ChunkFwdArgs {
     const void *s_in; const int64_t *s_map; int s_kinds; int s_dtype; void *s_out;
     __nv_bfloat16 *ckpt;  // optional [B*H][T/64][64*64] bf16 chunk-start states in operand (swizzled) layout
     int B, T, H;
+    bool write_y;         // false: only states / checkpoints are produced
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -385,8 +386,10 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
         tc_fence_before_sync();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
         if (tid == 0) {
-            tma_store_3d(&tm_y, sAM, h * 64, c * kChunk, b);
-            bulk_commit();
+            if (a.write_y) {
+                tma_store_3d(&tm_y, sAM, h * 64, c * kChunk, b);
+                bulk_commit();
+            }
             if (c + 2 < nchunks) { issue_loads(c + 2); ++loads_pending; }
         }
     }

@@ -103,3 +103,50 @@ def test_operator_autograd_bf16(pkg):
     for n in got:
         assert scaled_err(got[n], ref[n]) <= TOL_BF16, n
     assert status(pkg) == 0
+
+
+@pytest.mark.parametrize("B,T,H,with_ckpt", [(1, 64, 1, True), (2, 128, 2, True), (1, 320, 2, False), (2, 1000, 1, True),
+                                             (1, 1, 1, True), (1, 65, 1, False), (2, 4096, 2, True)])
+def test_backward_vs_oracle(pkg, B, T, H, with_ckpt):
+    d = O.make_inputs(B, T, H, N, seed=31 + T + H)
+    t = dev_inputs(d)
+    ckpt = None
+    if with_ckpt:
+        _, _, ckpt = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_ckpt=True, variant=pkg.VARIANT_CHUNK)
+        assert ckpt is not None
+    g = pkg.backward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], t["gy"], N, ckpt=ckpt, variant=pkg.VARIANT_CHUNK)
+    torch.cuda.synchronize()
+    assert status(pkg) == 0
+    dr = rounded(d, torch.bfloat16)
+    ref = c_oracle.bwd(dr["r"], dr["k"], dr["v"], dr["w"], dr["u"], dr["gy"], N)
+    for name, got, want in zip(("gr", "gk", "gv", "gw", "gu"), g, ref):
+        got = np_(got)
+        assert np.isfinite(got).all(), name
+        if np.abs(want).max() == 0:
+            assert np.abs(got).max() == 0, name
+        else:
+            assert scaled_err(got, want) <= TOL_BF16, f"{name}: {scaled_err(got, want):.3e}"
+
+
+def test_backward_extreme_decay(pkg):
+    B, T, H = 1, 192, 2
+    d = O.make_inputs(B, T, H, N, seed=41)
+    d["w"][:, 10:20] = -1e9
+    d["w"][:, 70:75] = 3.0
+    d["w"][:, 100] = 8.0
+    t = dev_inputs(d)
+    g = pkg.backward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], t["gy"], N, variant=pkg.VARIANT_CHUNK)
+    dr = rounded(d, torch.bfloat16)
+    ref = c_oracle.bwd(dr["r"], dr["k"], dr["v"], dr["w"], dr["u"], dr["gy"], N)
+    for name, got, want in zip(("gr", "gk", "gv", "gw", "gu"), g, ref):
+        assert np.isfinite(np_(got)).all(), name
+        assert scaled_err(np_(got), want) <= TOL_BF16, f"{name}: {scaled_err(np_(got), want):.3e}"
+
+
+def test_backward_bit_identical_reruns(pkg):
+    d = O.make_inputs(2, 256, 2, N, seed=42)
+    t = dev_inputs(d)
+    a = pkg.backward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], t["gy"], N, variant=pkg.VARIANT_CHUNK)
+    b = pkg.backward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], t["gy"], N, variant=pkg.VARIANT_CHUNK)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
