@@ -9,7 +9,8 @@ import ctypes
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libwkv6_b200.so")
+# WKV6_B200_LIB selects another build of the same library (e.g. one compiled with extra instrumentation)
+LIB_PATH = os.environ.get("WKV6_B200_LIB") or os.path.join(PKG, "libwkv6_b200.so")
 
 BF16, F16, F32 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SEQ, VARIANT_CHUNK = 0, 1, 2

@@ -60,7 +60,7 @@ int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const voi
     cudaError_t e = cudaFuncSetAttribute(chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ChunkFwdSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_fwd_kernel)");
-    chunk_fwd_kernel<<<p->B * p->H, 128, ChunkFwdSmem::kAlloc, st>>>(mr, mk, mv, mw, my, a);
+    chunk_fwd_kernel<<<p->B * p->H, 256, ChunkFwdSmem::kAlloc, st>>>(mr, mk, mv, mw, my, a);
     e = cudaGetLastError();
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_fwd_kernel launch");
 }
@@ -110,3 +110,9 @@ int chunk_status() {
 }
 
 }  // namespace wkv6
+
+#ifdef WKV6_TIMING
+extern "C" __attribute__((visibility("default"))) int wkv6_debug_timing(long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, wkv6::g_chunk_timing, sizeof(long long) * 64 * 16);
+}
+#endif

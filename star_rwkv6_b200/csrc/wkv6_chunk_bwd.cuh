@@ -86,12 +86,8 @@ __device__ __forceinline__ void umma_ss_masked(uint32_t d_tmem, uint64_t adesc, 
 
 __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, float (&f)[16]) {
     uint32_t v[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    ptx::tmem_ld_16x256b_x4(taddr, v);
+    ptx::tmem_wait_ld();
 #pragma unroll
     for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
 }
@@ -217,8 +213,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     bool load_pending = true;  // thread 0
     for (int it = 0; it < nchunks; ++it) {
         const int c = nchunks - 1 - it;
+        WKV6_TSTAMP(it, 0);
         if (!mbar_wait(bar_full, it & 1)) err = 1;
         if (tid == 0) load_pending = false;
+        WKV6_TSTAMP(it, 1);
 
         // ---- per-step log2 decays and their running sums inside the block (fragment layout)
         uint32_t rp[8], kp[8];  // raw r, k as packed bf16 pairs: index 2*nn + (0: row ta, 1: row ta+8)
@@ -260,6 +258,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         if (tid < 64) sT1[tid] = 0.f;  // accumulated in epilogue 1
         if (tid == 0) bulk_wait_read<0>();  // the previous chunk's output tiles have left shared memory
         if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
+        WKV6_TSTAMP(it, 2);
 
         // ---- per (block, channel) factors, one pair per thread
         {
@@ -278,6 +277,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
             if (J == 0) sDtot[i] = ex2f(all);
         }
         __syncthreads();
+        WKV6_TSTAMP(it, 3);
 
         // ---- scaled operands
         {
@@ -335,6 +335,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
+        WKV6_TSTAMP(it, 4);
 
         // ---- MMA group 1
         if (tid == 0) {
@@ -369,8 +370,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 umma_ss(tmGV, umma_desc_sw128(aKH + 32 * kk), umma_desc_sw128(aAB + 2048 * kk), idKM, kk > 0);
             umma_commit(bar_mma1);
         }
+        WKV6_TSTAMP(it, 5);
         if (!mbar_wait(bar_mma1, it & 1)) err = 2;
         tc_fence_after_sync();
+        WKV6_TSTAMP(it, 6);
 
         // ---- epilogue 1: masked P and A as bf16 operands, reverse-state update
         {
@@ -435,6 +438,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         fence_proxy_async_smem();
         tc_fence_before_sync();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 11; break; }
+        WKV6_TSTAMP(it, 7);
 
         // ---- MMA group 2
         if (tid == 0) {
@@ -462,8 +466,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 umma_ss(tmGV, umma_desc_sw128(aAM + 2048 * kk), umma_desc_sw128(aG + 2048 * kk), idMM, true);
             umma_commit(bar_mma2);
         }
+        WKV6_TSTAMP(it, 8);
         if (!mbar_wait(bar_mma2, it & 1)) err = 3;
         tc_fence_after_sync();
+        WKV6_TSTAMP(it, 9);
         // every input tile is dead once the second MMA group has completed: fetch the next chunk now
         if (tid == 0 && c > 0 && err == 0) { issue_loads(c - 1); load_pending = true; }
 
@@ -559,6 +565,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
             }
             tc_fence_before_sync();
             __syncthreads();
+            WKV6_TSTAMP(it, 10);
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 const int col = 8 * (n0 + nn) + 2 * q;
@@ -589,6 +596,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         }
         fence_proxy_async_smem();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
+        WKV6_TSTAMP(it, 11);
         if (tid == 0) {
             tma_store_3d(&tm_gr, sP, h * 64, c * kChunk, b);
             tma_store_3d(&tm_gk, sAM, h * 64, c * kChunk, b);

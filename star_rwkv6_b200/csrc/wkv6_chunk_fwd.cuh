@@ -36,6 +36,15 @@ constexpr float kMinLogDecay2 = -10.0f * 1.4426950408889634f;  // clamp of the p
 // device-side error word: 0 = fine, otherwise the code of the wait that ran out
 __device__ int g_chunk_status;
 
+// Phase timestamps of CTA 0 (builds with -DWKV6_TIMING only): g_chunk_timing[chunk][phase] = clock64()
+#ifdef WKV6_TIMING
+__device__ long long g_chunk_timing[64][16];
+#define WKV6_TSTAMP(iter, k) \
+    do { if (blockIdx.x == 0 && threadIdx.x == 0 && (iter) < 64) g_chunk_timing[(iter)][(k)] = clock64(); } while (0)
+#else
+#define WKV6_TSTAMP(iter, k) do { } while (0)
+#endif
+
 struct ChunkFwdSmem {
     static constexpr int kStage = 4 * kTile;                 // r, k, v, w
     static constexpr int oStage0 = 0;
@@ -77,34 +86,39 @@ __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
-__global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_r,
-                                                        const __grid_constant__ CUtensorMap tm_k,
-                                                        const __grid_constant__ CUtensorMap tm_v,
-                                                        const __grid_constant__ CUtensorMap tm_w,
-                                                        const __grid_constant__ CUtensorMap tm_y,
-                                                        const ChunkFwdArgs a) {
+__global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_r,
+                                                           const __grid_constant__ CUtensorMap tm_k,
+                                                           const __grid_constant__ CUtensorMap tm_v,
+                                                           const __grid_constant__ CUtensorMap tm_w,
+                                                           const __grid_constant__ CUtensorMap tm_y,
+                                                           const ChunkFwdArgs a) {
     using namespace ptx;
     using SM = ChunkFwdSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *sKH = smem + SM::oKH, *sKD = smem + SM::oKD, *sAM = smem + SM::oAM, *sSB = smem + SM::oSB;
-    float *sHead = reinterpret_cast<float *>(smem + SM::oHead);
-    float *sTot = reinterpret_cast<float *>(smem + SM::oTot);
+    float *sHead = reinterpret_cast<float *>(smem + SM::oHead);  // [4][64] log2-decay sum of tokens 0..7 of a block
+    float *sTail = reinterpret_cast<float *>(smem + SM::oTot);   // [4][64] log2-decay sum of tokens 8..15 of a block
     float *sDtot = reinterpret_cast<float *>(smem + SM::oDtot);
     float *sBonus = reinterpret_cast<float *>(smem + SM::oBonus);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SM::oBar);
     uint64_t *bar_full = bars, *bar_mma1 = bars + 2, *bar_mma2 = bars + 3;
     uint32_t *slot = reinterpret_cast<uint32_t *>(smem + SM::oSlot);
 
+    // Thread roles.  Operand pass: warp (w4, half) owns tokens 16*w4 + 8*half .. +7, lane = channel pair.
+    // Accumulator passes: warp (w4, half) owns rows 16*w4 + r0 (+8) and the 32 columns 32*half .. +31
+    // (fragment layout of tcgen05.ld.16x256b: columns 8n + 2q, +1).
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int w4 = warp & 3, half = warp >> 2, n0 = 4 * half;
+    const int q = lane & 3, r0 = lane >> 2;
+    const int ta = 16 * w4 + r0;
     const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
     const int nchunks = (a.T + kChunk - 1) / kChunk;
-    const int q = lane & 3, r0 = lane >> 2;  // accumulator fragment coordinates
 
     if (tid == 0) {
         mbar_init(&bar_full[0], 1);
         mbar_init(&bar_full[1], 1);
-        mbar_init(bar_mma1, 1);
+        mbar_init(bar_mma1, 2);  // two issuing threads
         mbar_init(bar_mma2, 1);
         fence_mbar_init();
         prefetch_tensormap(&tm_r); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
@@ -115,8 +129,8 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
         tmem_relinquish();
     }
 
-    // state in accumulator-fragment layout: rows i = 16*warp + r0 (+8), columns j = 8n + 2q (+1)
-    float S[32];
+    // state in accumulator-fragment layout: rows i = ta (+8), columns j = 8(n0+nn) + 2q (+1)
+    float S[16];
     {
         const bool has = a.s_in != nullptr;
         size_t so = 0;
@@ -126,17 +140,15 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
             so = ((size_t)kind * a.H + h) * 4096;
         }
 #pragma unroll
-        for (int n = 0; n < 8; ++n)
+        for (int nn = 0; nn < 4; ++nn) {
+            const int j = 8 * (n0 + nn) + 2 * q;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int i = 16 * warp + r0 + (e >= 2 ? 8 : 0), j = 8 * n + 2 * q + (e & 1);
-                S[4 * n + e] = has ? load_any(a.s_in, a.s_dtype, so + (size_t)i * 64 + j) : 0.f;
+                const int i = ta + (e >= 2 ? 8 : 0);
+                S[4 * nn + e] = has ? load_any(a.s_in, a.s_dtype, so + (size_t)i * 64 + j + (e & 1)) : 0.f;
             }
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const int i0 = 16 * warp + r0, j = 8 * n + 2 * q;
-            *reinterpret_cast<uint32_t *>(sSB + sw128_off(i0, j)) = pack_bf2(S[4 * n], S[4 * n + 1]);
-            *reinterpret_cast<uint32_t *>(sSB + sw128_off(i0 + 8, j)) = pack_bf2(S[4 * n + 2], S[4 * n + 3]);
+            *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta, j)) = pack_bf2(S[4 * nn], S[4 * nn + 1]);
+            *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta + 8, j)) = pack_bf2(S[4 * nn + 2], S[4 * nn + 3]);
         }
     }
     const float2 u2 = make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane),
@@ -148,7 +160,8 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
     tc_fence_after_sync();
     const uint32_t tb = *slot;
     const uint32_t tmA0 = tb, tmY = tb + 64, tmS = tb + 128, tmAD = tb + (16u << 16);
-    const uint32_t wl = (uint32_t)(warp * 32) << 16;
+    const uint32_t wl = (uint32_t)(w4 * 32) << 16;  // this warp's TMEM lane quarter
+    const uint32_t cb = 8 * n0;                     // first accumulator column of this thread's fragment
 
     auto issue_loads = [&](int c) {
         const int st = c & 1;
@@ -172,22 +185,31 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
     constexpr uint32_t idKK96 = umma_idesc_bf16(64, 96, false, false);
     constexpr uint32_t idMM = umma_idesc_bf16(64, 64, true, true);
     constexpr uint32_t idKM = umma_idesc_bf16(64, 64, false, true);
+    // operand descriptors of stage 0; a step of 16 along K is +2 (K-major, 32 bytes) or +128 (MN-major, 2048 bytes)
+    // in the 16-byte units of the address field, the second stage is +kStage/16
+    const uint64_t dR = umma_desc_sw128(smem_u32(smem)), dK = umma_desc_sw128(smem_u32(smem + kTile));
+    const uint64_t dV = umma_desc_sw128(smem_u32(smem + 2 * kTile)), dW = umma_desc_sw128(smem_u32(smem + 3 * kTile));
+    const uint64_t dKH = umma_desc_sw128(smem_u32(sKH)), dKD = umma_desc_sw128(smem_u32(sKD));
+    const uint64_t dAM = umma_desc_sw128(smem_u32(sAM)), dSB = umma_desc_sw128(smem_u32(sSB));
 
     int err = 0;
     int loads_pending = (nchunks > 1) ? 2 : 1;  // meaningful on thread 0 only
     for (int c = 0; c < nchunks; ++c) {
         const int st = c & 1;
-        uint8_t *sR = smem + st * SM::kStage, *sK = sR + kTile, *sV = sR + 2 * kTile, *sW = sR + 3 * kTile;
+        uint8_t *sR = smem + st * SM::kStage, *sK = sR + kTile, *sW = sR + 3 * kTile;
+        const uint64_t so = (uint64_t)(st * (SM::kStage >> 4));
+        WKV6_TSTAMP(c, 0);
         if (!mbar_wait(&bar_full[st], (c >> 1) & 1)) err = 1;
         if (tid == 0) --loads_pending;
+        WKV6_TSTAMP(c, 1);
 
-        // ---- pass 1: per-step log2 decays of this thread's 16 tokens x 2 channels, inclusive running sums
-        float2 x[16];
+        // ---- pass 1: per-step log2 decays of this thread's 8 tokens x 2 channels, running sums from the first of them
+        float2 x[8];
         {
             float2 cs = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int tt = 0; tt < 16; ++tt) {
-                const int t = 16 * warp + tt;
+            for (int tt = 0; tt < 8; ++tt) {
+                const int t = 16 * w4 + 8 * half + tt;
                 const float2 w2 = ld_bf2(sW + sw128_off(t, 2 * lane));
                 float lx = fmaxf(-ex2f(w2.x * kLog2e) * kLog2e, kMinLogDecay2);
                 float ly = fmaxf(-ex2f(w2.y * kLog2e) * kLog2e, kMinLogDecay2);
@@ -195,55 +217,60 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
                 cs.x += lx; cs.y += ly;
                 x[tt] = cs;
             }
-            *reinterpret_cast<float2 *>(&sHead[warp * 64 + 2 * lane]) = x[7];
-            *reinterpret_cast<float2 *>(&sTot[warp * 64 + 2 * lane]) = x[15];
+            *reinterpret_cast<float2 *>(&(half ? sTail : sHead)[w4 * 64 + 2 * lane]) = cs;
         }
         // the previous chunk's y tile and checkpoint copies must have left shared memory before it is rewritten
         if (tid == 0) bulk_wait_read<0>();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
+        WKV6_TSTAMP(c, 2);
 
-        // ---- pass 2: scaled operands
+        // ---- pass 2: scaled operands.  The block reference is the boundary between the two token halves, so the
+        // running sums of the second half are already relative to it and those of the first half need only -head.
         {
-            float2 pre = make_float2(0.f, 0.f), post = make_float2(0.f, 0.f);
+            float2 pre = make_float2(0.f, 0.f), post = make_float2(0.f, 0.f), head, tail;
+            head = tail = make_float2(0.f, 0.f);
+            float2 totJ[4], headJ[4];
 #pragma unroll
             for (int J = 0; J < 4; ++J) {
-                const float2 tj = *reinterpret_cast<const float2 *>(&sTot[J * 64 + 2 * lane]);
-                if (J < warp) { pre.x += tj.x; pre.y += tj.y; }
-                if (J > warp) { post.x += tj.x; post.y += tj.y; }
+                headJ[J] = *reinterpret_cast<const float2 *>(&sHead[J * 64 + 2 * lane]);
+                const float2 tl = *reinterpret_cast<const float2 *>(&sTail[J * 64 + 2 * lane]);
+                totJ[J] = make_float2(headJ[J].x + tl.x, headJ[J].y + tl.y);
+                if (J < w4) { pre.x += totJ[J].x; pre.y += totJ[J].y; }
+                if (J > w4) { post.x += totJ[J].x; post.y += totJ[J].y; }
+                if (J == w4) { head = headJ[J]; tail = tl; }
             }
-            const float2 myhead = x[7], mytot = x[15];
-            const float2 tail = make_float2(mytot.x - myhead.x, mytot.y - myhead.y);
-            const float2 fR = make_float2(ex2f(myhead.x + pre.x), ex2f(myhead.y + pre.y));
+            const float2 base = half ? make_float2(0.f, 0.f) : head;
+            const float2 fR = make_float2(ex2f(head.x + pre.x), ex2f(head.y + pre.y));
             const float2 fK = make_float2(ex2f(tail.x + post.x), ex2f(tail.y + post.y));
-            // factors of the k~ copies for block distances 1..3 (only those with warp + delta <= 3 exist)
+            // factors of the k~ copies for block distances 1..3 (only those with w4 + delta <= 3 exist)
             float2 fD[3];
             {
                 float2 acc = tail;
 #pragma unroll
                 for (int dl = 1; dl <= 3; ++dl) {
-                    const int Jt = warp + dl;  // the row block these copies serve
-                    if (Jt <= 3) {
-                        const float2 hj = *reinterpret_cast<const float2 *>(&sHead[Jt * 64 + 2 * lane]);
-                        const float2 tj = *reinterpret_cast<const float2 *>(&sTot[Jt * 64 + 2 * lane]);
-                        fD[dl - 1] = make_float2(ex2f(acc.x + hj.x), ex2f(acc.y + hj.y));
-                        acc.x += tj.x; acc.y += tj.y;
-                    } else {
-                        fD[dl - 1] = make_float2(0.f, 0.f);
+                    fD[dl - 1] = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int Jt = 1; Jt < 4; ++Jt) {
+                        if (Jt == w4 + dl) {
+                            fD[dl - 1] = make_float2(ex2f(acc.x + headJ[Jt].x), ex2f(acc.y + headJ[Jt].y));
+                            acc.x += totJ[Jt].x; acc.y += totJ[Jt].y;
+                        }
                     }
                 }
             }
             if (warp == 0) {
-                const float2 all = make_float2(mytot.x + post.x, mytot.y + post.y);
+                const float2 all = make_float2(head.x + tail.x + post.x, head.y + tail.y + post.y);
                 *reinterpret_cast<float2 *>(&sDtot[2 * lane]) = make_float2(ex2f(all.x), ex2f(all.y));
             }
-            float bon[16];
+            float bon[8];
+            const uint32_t csw = (uint32_t)(2 * lane);  // channel offset before swizzling
 #pragma unroll
-            for (int tt = 0; tt < 16; ++tt) {
-                const int t = 16 * warp + tt;
-                const uint32_t off = sw128_off(t, 2 * lane);
+            for (int tt = 0; tt < 8; ++tt) {
+                const int t = 16 * w4 + 8 * half + tt;
+                const uint32_t off = sw128_off(t, csw);
                 const float2 xp = (tt == 0) ? make_float2(0.f, 0.f) : x[tt - 1];
-                const float2 er = make_float2(ex2f(xp.x - myhead.x), ex2f(xp.y - myhead.y));
-                const float2 ek = make_float2(ex2f(myhead.x - x[tt].x), ex2f(myhead.y - x[tt].y));
+                const float2 er = make_float2(ex2f(xp.x - base.x), ex2f(xp.y - base.y));
+                const float2 ek = make_float2(ex2f(base.x - x[tt].x), ex2f(base.y - x[tt].y));
                 const float2 r2 = ld_bf2(sR + off), k2 = ld_bf2(sK + off);
                 bon[tt] = r2.x * u2.x * k2.x + r2.y * u2.y * k2.y;
                 const float2 rt = make_float2(r2.x * er.x, r2.y * er.y);
@@ -252,57 +279,65 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
                 st_bf2(sW + off, rt.x * fR.x, rt.y * fR.y);         // r^  (A operand against the incoming state)
                 st_bf2(sK + off, kt.x, kt.y);                       // k~  distance 0
                 st_bf2(sKH + off, kt.x * fK.x, kt.y * fK.y);        // k^  (state increment)
-                if (warp <= 2) st_bf2(sKD + off, kt.x * fD[0].x, kt.y * fD[0].y);                 // rows [0,48)
-                if (warp <= 1) st_bf2(sKD + 48 * 128 + off, kt.x * fD[1].x, kt.y * fD[1].y);      // rows [48,80)
-                if (warp == 0) st_bf2(sKD + 80 * 128 + off, kt.x * fD[2].x, kt.y * fD[2].y);      // rows [80,96)
+                if (w4 <= 2) st_bf2(sKD + off, kt.x * fD[0].x, kt.y * fD[0].y);                 // rows [0,48)
+                if (w4 <= 1) st_bf2(sKD + 48 * 128 + off, kt.x * fD[1].x, kt.y * fD[1].y);      // rows [48,80)
+                if (w4 == 0) st_bf2(sKD + 80 * 128 + off, kt.x * fD[2].x, kt.y * fD[2].y);      // rows [80,96)
             }
-            // sum the bonus partials over the 32 channel pairs: 16 values across 32 lanes in 16 shuffles
+            // sum the bonus partials over the 32 channel pairs: 8 values across 32 lanes in 9 shuffles
 #pragma unroll
-            for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
+            for (int hf = 4, bit = 16; hf >= 1; hf >>= 1, bit >>= 1) {
                 const bool up = (lane & bit) != 0;
 #pragma unroll
-                for (int i2 = 0; i2 < half; ++i2) {
-                    const float send = up ? bon[i2] : bon[i2 + half];
-                    const float keep = up ? bon[i2 + half] : bon[i2];
+                for (int i2 = 0; i2 < hf; ++i2) {
+                    const float send = up ? bon[i2] : bon[i2 + hf];
+                    const float keep = up ? bon[i2 + hf] : bon[i2];
                     bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
                 }
             }
+            bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 2);
             bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 1);
-            if ((lane & 1) == 0) {
-                const int tok = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
-                sBonus[16 * warp + tok] = bon[0];
+            if ((lane & 3) == 0) {
+                const int tok = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                sBonus[16 * w4 + 8 * half + tok] = bon[0];
             }
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
+        WKV6_TSTAMP(c, 3);
 
         if (tid == 0) {
             tc_fence_after_sync();
-            const uint32_t aR = smem_u32(sR), aK = smem_u32(sK), aV = smem_u32(sV), aW = smem_u32(sW);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // A (distance 0) = r~ k~^T
-                umma_ss(tmA0, umma_desc_sw128(aR + 32 * kk), umma_desc_sw128(aK + 32 * kk), idKK, kk > 0);
+                umma_ss(tmA0, dR + so + 2 * kk, dK + so + 2 * kk, idKK, kk > 0);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // A (distances 1..3) = r~ [k~ copies]^T
-                umma_ss(tmAD, umma_desc_sw128(aR + 32 * kk), umma_desc_sw128(smem_u32(sKD) + 32 * kk), idKK96, kk > 0);
+                umma_ss(tmAD, dR + so + 2 * kk, dKD + 2 * kk, idKK96, kk > 0);
+            umma_commit(bar_mma1);
+        } else if (tid == 32) {
+            tc_fence_after_sync();
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // state increment = k^^T v
-                umma_ss(tmS, umma_desc_sw128(smem_u32(sKH) + 2048 * kk), umma_desc_sw128(aV + 2048 * kk), idMM, kk > 0);
+                umma_ss(tmS, dKH + 128 * kk, dV + so + 128 * kk, idMM, kk > 0);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // y = r^ S_in
-                umma_ss(tmY, umma_desc_sw128(aW + 32 * kk), umma_desc_sw128(smem_u32(sSB) + 2048 * kk), idKM, kk > 0);
+                umma_ss(tmY, dW + so + 2 * kk, dSB + 128 * kk, idKM, kk > 0);
             umma_commit(bar_mma1);
         }
+        WKV6_TSTAMP(c, 4);
         if (!mbar_wait(bar_mma1, c & 1)) err = 2;
         tc_fence_after_sync();
+        WKV6_TSTAMP(c, 5);
 
-        // ---- epilogue of the intra-chunk matrix: pick, mask, round, store as the A operand of A v
+        // ---- epilogue of the intra-chunk matrix: pick, mask, round, store as the A operand of A v.
+        // This warp covers column blocks J = 2*half and 2*half + 1 of row block I = w4.
         {
-            const int I = warp;
+            const int I = w4;
 #pragma unroll
-            for (int J = 0; J < 4; ++J) {
-                uint32_t o0 = 0, o1 = 0, o2 = 0, o3 = 0;  // (row r0: cols 2q,2q+1 | 8+2q,..) and the same for row r0+8
+            for (int jj = 0; jj < 2; ++jj) {
+                const int J = 2 * half + jj;
+                uint32_t o0 = 0, o1 = 0, o2 = 0, o3 = 0;  // (row ta: cols 2q,2q+1 | 8+2q,..) and the same for row ta+8
                 if (J <= I) {
                     const int dl = I - J;
                     const uint32_t src = (dl == 0) ? (tmA0 + wl + 16 * J)
@@ -324,33 +359,34 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
                     o0 = pack_bf2(f[0], f[1]); o2 = pack_bf2(f[2], f[3]);
                     o1 = pack_bf2(f[4], f[5]); o3 = pack_bf2(f[6], f[7]);
                 }
-                const int t0r = 16 * I + r0, s0 = 16 * J + 2 * q;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r, s0)) = o0;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r, s0 + 8)) = o1;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r + 8, s0)) = o2;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r + 8, s0 + 8)) = o3;
+                const int s0 = 16 * J + 2 * q;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta, s0)) = o0;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta, s0 + 8)) = o1;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta + 8, s0)) = o2;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta + 8, s0 + 8)) = o3;
             }
         }
         // ---- state update in registers and its bf16 operand copy for the next chunk
         {
-            uint32_t v32[32];
-            tmem_ld_16x256b_x8(tmS + wl, v32);
+            uint32_t v16[16];
+            tmem_ld_16x256b_x4(tmS + wl + cb, v16);
             tmem_wait_ld();
-            const float d0 = sDtot[16 * warp + r0], d1 = sDtot[16 * warp + r0 + 8];
+            const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
 #pragma unroll
-            for (int n = 0; n < 8; ++n) {
-                S[4 * n + 0] = fmaf(S[4 * n + 0], d0, __uint_as_float(v32[4 * n + 0]));
-                S[4 * n + 1] = fmaf(S[4 * n + 1], d0, __uint_as_float(v32[4 * n + 1]));
-                S[4 * n + 2] = fmaf(S[4 * n + 2], d1, __uint_as_float(v32[4 * n + 2]));
-                S[4 * n + 3] = fmaf(S[4 * n + 3], d1, __uint_as_float(v32[4 * n + 3]));
-                const int i0 = 16 * warp + r0, j = 8 * n + 2 * q;
-                *reinterpret_cast<uint32_t *>(sSB + sw128_off(i0, j)) = pack_bf2(S[4 * n], S[4 * n + 1]);
-                *reinterpret_cast<uint32_t *>(sSB + sw128_off(i0 + 8, j)) = pack_bf2(S[4 * n + 2], S[4 * n + 3]);
+            for (int nn = 0; nn < 4; ++nn) {
+                S[4 * nn + 0] = fmaf(S[4 * nn + 0], d0, __uint_as_float(v16[4 * nn + 0]));
+                S[4 * nn + 1] = fmaf(S[4 * nn + 1], d0, __uint_as_float(v16[4 * nn + 1]));
+                S[4 * nn + 2] = fmaf(S[4 * nn + 2], d1, __uint_as_float(v16[4 * nn + 2]));
+                S[4 * nn + 3] = fmaf(S[4 * nn + 3], d1, __uint_as_float(v16[4 * nn + 3]));
+                const int j = 8 * (n0 + nn) + 2 * q;
+                *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta, j)) = pack_bf2(S[4 * nn], S[4 * nn + 1]);
+                *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta + 8, j)) = pack_bf2(S[4 * nn + 2], S[4 * nn + 3]);
             }
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 11; break; }
+        WKV6_TSTAMP(c, 6);
 
         if (tid == 0) {
             tc_fence_after_sync();
@@ -362,29 +398,32 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
             }
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // y += A v
-                umma_ss(tmY, umma_desc_sw128(smem_u32(sAM) + 32 * kk), umma_desc_sw128(smem_u32(sV) + 2048 * kk), idKM, true);
+                umma_ss(tmY, dAM + 2 * kk, dV + so + 128 * kk, idKM, true);
             umma_commit(bar_mma2);
         }
+        WKV6_TSTAMP(c, 7);
         if (!mbar_wait(bar_mma2, c & 1)) err = 3;
         tc_fence_after_sync();
+        WKV6_TSTAMP(c, 8);
 
         // ---- y epilogue: round to bf16 into the (now free) A tile, one TMA store per chunk
         {
-            uint32_t v32[32];
-            tmem_ld_16x256b_x8(tmY + wl, v32);
+            uint32_t v16[16];
+            tmem_ld_16x256b_x4(tmY + wl + cb, v16);
             tmem_wait_ld();
 #pragma unroll
-            for (int n = 0; n < 8; ++n) {
-                const int t0r = 16 * warp + r0, j = 8 * n + 2 * q;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r, j)) =
-                    pack_bf2(__uint_as_float(v32[4 * n]), __uint_as_float(v32[4 * n + 1]));
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(t0r + 8, j)) =
-                    pack_bf2(__uint_as_float(v32[4 * n + 2]), __uint_as_float(v32[4 * n + 3]));
+            for (int nn = 0; nn < 4; ++nn) {
+                const int j = 8 * (n0 + nn) + 2 * q;
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta, j)) =
+                    pack_bf2(__uint_as_float(v16[4 * nn]), __uint_as_float(v16[4 * nn + 1]));
+                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta + 8, j)) =
+                    pack_bf2(__uint_as_float(v16[4 * nn + 2]), __uint_as_float(v16[4 * nn + 3]));
             }
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
+        WKV6_TSTAMP(c, 9);
         if (tid == 0) {
             if (a.write_y) {
                 tma_store_3d(&tm_y, sAM, h * 64, c * kChunk, b);
@@ -399,8 +438,7 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
         if (err != 0) {
             // loads still in flight target this CTA's shared memory: wait for them (bounded) before leaving
             for (int st = 0; st < 2 && loads_pending > 0; ++st) {
-                // parity unknown after an error: poll both
-                for (uint32_t it = 0; it < (1u << 16); ++it)
+                for (uint32_t it = 0; it < (1u << 16); ++it)  // parity unknown after an error: poll both
                     if (mbar_try_wait(&bar_full[st], 0) || mbar_try_wait(&bar_full[st], 1)) break;
             }
             atomicExch(&g_chunk_status, err);
@@ -408,13 +446,13 @@ __global__ void __launch_bounds__(128) chunk_fwd_kernel(const __grid_constant__ 
         bulk_wait<0>();
     }
     if (err == 0 && a.s_out != nullptr) {
-        const size_t so = (size_t)blockIdx.x * 4096;
+        const size_t so2 = (size_t)blockIdx.x * 4096;
 #pragma unroll
-        for (int n = 0; n < 8; ++n)
+        for (int nn = 0; nn < 4; ++nn)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int i = 16 * warp + r0 + (e >= 2 ? 8 : 0), j = 8 * n + 2 * q + (e & 1);
-                store_any(a.s_out, a.s_dtype, so + (size_t)i * 64 + j, S[4 * n + e]);
+                const int i = ta + (e >= 2 ? 8 : 0), j = 8 * (n0 + nn) + 2 * q + (e & 1);
+                store_any(a.s_out, a.s_dtype, so2 + (size_t)i * 64 + j, S[4 * nn + e]);
             }
     }
     tc_fence_before_sync();
