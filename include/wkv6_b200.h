@@ -111,6 +111,31 @@ WKV6_API int wkv6_backward(const wkv6_problem *p, const void *r, const void *k, 
 
 WKV6_API size_t wkv6_backward_workspace_bytes(const wkv6_problem *p, int have_ckpt);
 
+/*
+ * Backward without any caller-provided scratch.  It has no counterpart in the reference.
+ *
+ * Some hosts of this library may not allocate device memory around a call and have no buffer to lend it: a
+ * handler for XLA's legacy custom-call ABI sees only the operand and result buffers XLA planned
+ * (rwkv_backward_fn has eleven of them and no workspace), and code running under a fixed memory plan or inside
+ * a region where the CUDA allocator must not be entered is in the same position.  For them this entry point
+ * runs the sequential backward (always that variant, whatever p->variant says) with its fp32 scratch - one
+ * value per (token, channel) - taken from an array that is compiled into the library image.
+ *
+ *   - Limit: B*T*H*N <= wkv6_static_scratch_bytes()/4 = 8 388 608 (32 MiB of scratch).  Larger problems are
+ *     rejected with WKV6_ERR_WORKSPACE and a message; use wkv6_backward with a workspace for them.
+ *   - The array costs 32 MiB on every GPU that loads the library, for the life of the process.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call outside any stream capture.  No call allocates or frees memory.
+ *   - All calls on one device share the one array and it keeps whatever the last call left in it.  Nothing in it
+ *     needs clearing between calls (each call overwrites what it later reads), but two calls whose kernels
+ *     overlap on the GPU - different streams, or different host threads - would corrupt each other: order them.
+ * Arguments and results are those of wkv6_backward.
+ */
+WKV6_API int wkv6_backward_static_scratch(const wkv6_problem *p, const void *r, const void *k, const void *v,
+                                          const void *w, const void *u, const void *gy, void *gr, void *gk, void *gv,
+                                          void *gw, void *gu, void *stream);
+WKV6_API size_t wkv6_static_scratch_bytes(void);
+
 #ifdef __cplusplus
 }
 #endif

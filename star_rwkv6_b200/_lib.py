@@ -19,7 +19,7 @@ VARIANTS = {"auto": VARIANT_AUTO, "seq": VARIANT_SEQ, "chunk": VARIANT_CHUNK}
 # every symbol include/wkv6_b200.h declares
 SYMBOLS = (
     "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
-    "wkv6_backward", "wkv6_backward_workspace_bytes",
+    "wkv6_backward", "wkv6_backward_workspace_bytes", "wkv6_backward_static_scratch", "wkv6_static_scratch_bytes",
 )
 
 
@@ -62,6 +62,10 @@ def _load():
     lib.wkv6_backward.argtypes = [pp] + [vp] * 11 + [vp, vp, sz, vp]
     lib.wkv6_backward_workspace_bytes.restype = sz
     lib.wkv6_backward_workspace_bytes.argtypes = [pp, ctypes.c_int]
+    lib.wkv6_backward_static_scratch.restype = ctypes.c_int
+    lib.wkv6_backward_static_scratch.argtypes = [pp] + [vp] * 11 + [vp]
+    lib.wkv6_static_scratch_bytes.restype = sz
+    lib.wkv6_static_scratch_bytes.argtypes = []
     return lib
 
 
