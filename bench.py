@@ -205,11 +205,8 @@ def run_b200(a):
 
     B, T, H, N = a.B, a.T, a.H, a.N
     if a.scaling == "strong" and world > 1:
-        assert (B * H) % world == 0
-        if B % world == 0:
-            B = B // world          # contiguous batch rows per rank
-        else:
-            H = (B * H // world) // B  # head shard per rank
+        from star_rwkv6_b200 import sharding
+        B, H = sharding.make_plan(a.B, a.H, world).local_shape()  # each rank generates its own shard directly
     C = H * N
     xdt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
     variant = _lib.VARIANTS[a.variant]

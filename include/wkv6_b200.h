@@ -136,6 +136,23 @@ WKV6_API int wkv6_backward_static_scratch(const wkv6_problem *p, const void *r, 
                                           void *gw, void *gu, void *stream);
 WKV6_API size_t wkv6_static_scratch_bytes(void);
 
+/*
+ * XLA legacy custom-call surface.  The library also exports the C++ symbols gpu_ops::rwkv_forward_fn,
+ * gpu_ops::rwkv_backward_fn and gpu_ops::rwkv_forward_with_state_fn with the signature
+ *     void f(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len)
+ * and the buffer orders of the reference (rwkv_kernel/jax_kernel/kernels.h:44-53, rwkv_kernels.cu:451-508);
+ * they throw std::runtime_error on failure as the reference does for a bad descriptor.  The functions below are
+ * the same handlers with an error code instead of an exception, the descriptor packer that replaces
+ * gpu_ops.create_rwkv_descriptor (rwkv_kernel/jax_kernel/gpu_ops.cpp:33-36; returns the blob size, 28), and the
+ * handler addresses (0 forward, 1 backward, 2 forward_with_state) for "xla._CUSTOM_CALL_TARGET" capsules
+ * (replaces gpu_ops.get_rwkv_registrations, gpu_ops.cpp:20-29).
+ */
+WKV6_API int wkv6_xla_forward(void *stream, void **buffers, const char *opaque, size_t opaque_len);
+WKV6_API int wkv6_xla_backward(void *stream, void **buffers, const char *opaque, size_t opaque_len);
+WKV6_API int wkv6_xla_forward_with_state(void *stream, void **buffers, const char *opaque, size_t opaque_len);
+WKV6_API int wkv6_xla_descriptor(int B, int T, int C, int H, int S, int x_type, int y_type, char *out, size_t out_len);
+WKV6_API void *wkv6_xla_target(int which);
+
 #ifdef __cplusplus
 }
 #endif

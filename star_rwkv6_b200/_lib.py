@@ -20,6 +20,7 @@ VARIANTS = {"auto": VARIANT_AUTO, "seq": VARIANT_SEQ, "chunk": VARIANT_CHUNK}
 SYMBOLS = (
     "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
     "wkv6_backward", "wkv6_backward_workspace_bytes", "wkv6_backward_static_scratch", "wkv6_static_scratch_bytes",
+    "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_descriptor", "wkv6_xla_target",
 )
 
 
@@ -66,10 +67,27 @@ def _load():
     lib.wkv6_backward_static_scratch.argtypes = [pp] + [vp] * 11 + [vp]
     lib.wkv6_static_scratch_bytes.restype = sz
     lib.wkv6_static_scratch_bytes.argtypes = []
+    for name in ("wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state"):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [vp, ctypes.POINTER(vp), ctypes.c_char_p, sz]
+    lib.wkv6_xla_descriptor.restype = ctypes.c_int
+    lib.wkv6_xla_descriptor.argtypes = [ctypes.c_int] * 7 + [ctypes.c_char_p, sz]
+    lib.wkv6_xla_target.restype = vp
+    lib.wkv6_xla_target.argtypes = [ctypes.c_int]
     return lib
 
 
 lib = _load()
+
+
+def xla_descriptor(B, T, C, H, S, x_type, y_type) -> bytes:
+    """The 28-byte opaque blob of the legacy custom calls (replaces gpu_ops.create_rwkv_descriptor)."""
+    buf = ctypes.create_string_buffer(32)
+    n = lib.wkv6_xla_descriptor(B, T, C, H, int(bool(S)), x_type, y_type, buf, 32)
+    if n <= 0:
+        raise WKV6Error(n, lib.wkv6_last_error().decode())
+    return buf.raw[:n]
 
 
 def check(rc: int) -> None:
