@@ -42,6 +42,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     return false;
 }
 
+// Wait of a whole CTA on an mbarrier: warp 0 polls, every other warp sleeps on the CTA barrier instead of
+// spending issue slots on polling.  All threads must call it; the result is uniform.
+__device__ __forceinline__ bool cta_wait(uint64_t *bar, uint32_t parity, int warp) {
+    bool ok = true;
+    if (warp == 0) ok = mbar_wait(bar, parity);
+    return __syncthreads_and(ok) != 0;
+}
+
 // ---- proxies / fences ------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

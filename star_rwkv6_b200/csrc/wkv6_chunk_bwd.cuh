@@ -24,8 +24,8 @@
 // four), so the per-element decay factors computed before the MMAs are still in registers when the
 // accumulators come back.  Running sums along time are lane scans over the 8 lanes that share q.
 //
-// Tensor-memory map (256 columns): lanes 0-15: [0,64) P -> GR1 | [64,128) A -> GK1 | [128,192) GR2 | [192,256) GK2
-//                                  lanes 16-31: [0,64) Abar increment | [64,128) gv
+// Tensor-memory map (256 columns): lanes 0-15: [0,64) P -> GR1 | [64,128) A (distance 0) -> GK1 | [128,192) GR2 | [192,256) GK2
+//                                  lanes 16-31: [0,64) Abar increment | [64,128) gv | [128,224) A (distances 1..3)
 #pragma once
 
 #include "wkv6_chunk_fwd.cuh"
@@ -60,7 +60,7 @@ struct ChunkBwdSmem {
     static constexpr int oBar = oT1 + 256;          // full, mma1, mma2
     static constexpr int oSlot = oBar + 32;
     static constexpr int kBytes = oSlot + 16;
-    static constexpr int kAlloc = kBytes + 1008;  // the dynamic base is 16-byte aligned; the tiles need 1024
+    static constexpr int kAlloc = kBytes;
 };
 
 struct ChunkBwdArgs {
@@ -82,6 +82,14 @@ __device__ __forceinline__ void umma_ss_masked(uint32_t d_tmem, uint64_t adesc, 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)accumulate), "r"(m0), "r"(m1), "r"(m2), "r"(m3)
         : "memory");
+}
+
+// one repetition: 8 columns, 4 values per thread (rows r0 / r0+8 x columns 2q, 2q+1); no wait
+__device__ __forceinline__ void tmem_ld_16x256b_x1(uint32_t taddr, float (&f)[4]) {
+    uint32_t v0, v1, v2, v3;
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(taddr));
+    f[0] = __uint_as_float(v0); f[1] = __uint_as_float(v1); f[2] = __uint_as_float(v2); f[3] = __uint_as_float(v3);
 }
 
 __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, float (&f)[16]) {
@@ -131,8 +139,14 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                                                            const ChunkBwdArgs a) {
     using namespace ptx;
     using SM = ChunkBwdSmem;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Declared with the alignment the swizzled tiles need, so that the compiler keeps every access in the shared
+    // address space with 32-bit addresses; the base is verified once instead of being realigned by pointer math.
+    extern __shared__ __align__(1024) uint8_t wkv6_chunk_smem[];
+    uint8_t *const smem = wkv6_chunk_smem;
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(&g_chunk_status, 50);
+        return;
+    }
     uint8_t *sR = smem + SM::oR, *sK = smem + SM::oK, *sV = smem + SM::oV, *sW = smem + SM::oW, *sG = smem + SM::oG;
     uint8_t *sS = smem + SM::oS, *sKH = smem + SM::oKH, *sKD = smem + SM::oKD, *sRD = smem + SM::oRD;
     uint8_t *sP = smem + SM::oP, *sAM = smem + SM::oAM, *sAB = smem + SM::oAB;
@@ -156,8 +170,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
 
     if (tid == 0) {
         mbar_init(bar_full, 1);
-        mbar_init(bar_mma1, 1);
-        mbar_init(bar_mma2, 1);
+        mbar_init(bar_mma1, 4);  // four issuing threads
+        mbar_init(bar_mma2, 3);  // three issuing threads
         fence_mbar_init();
         prefetch_tensormap(&tm_r); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_w);
         prefetch_tensormap(&tm_gy); prefetch_tensormap(&tm_gr); prefetch_tensormap(&tm_gk);
@@ -167,7 +181,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         tmem_alloc(slot, 256);
         tmem_relinquish();
     }
-    // zero: the reverse state (registers + operand copy), Z, and the copy tiles whose unused rows are never written
+    // zero: the reverse state (registers + operand copy)
     float AB[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) AB[e] = 0.f;
@@ -175,11 +189,14 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     float gu_acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) gu_acc[e] = 0.f;
-    float u_c[8];  // u of this thread's channels
+    float2 u_c[4];  // u of this thread's channel pairs
+    uint32_t fo[8];  // byte offsets of this thread's fragment elements in a swizzled tile: [2*nn + (row ta+8 ? 1 : 0)]
 #pragma unroll
     for (int nn = 0; nn < 4; ++nn) {
-        u_c[2 * nn] = load_any(a.u, a.u_dtype, (size_t)h * 64 + 8 * (n0 + nn) + 2 * q);
-        u_c[2 * nn + 1] = load_any(a.u, a.u_dtype, (size_t)h * 64 + 8 * (n0 + nn) + 2 * q + 1);
+        const int col = 8 * (n0 + nn) + 2 * q;
+        u_c[nn] = make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + col), load_any(a.u, a.u_dtype, (size_t)h * 64 + col + 1));
+        fo[2 * nn] = sw128_off(ta, col);
+        fo[2 * nn + 1] = sw128_off(ta + 8, col);
     }
 
     fence_proxy_async_smem();
@@ -189,7 +206,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     const uint32_t tbase = *slot;
     const uint32_t lo = (uint32_t)(32 * w4) << 16;  // this warp's TMEM lane quarter
     const uint32_t tmP = tbase, tmA = tbase + 64, tmGR2 = tbase + 128, tmGK2 = tbase + 192;
-    const uint32_t tmAN = tbase + (16u << 16), tmGV = tbase + (16u << 16) + 64;
+    const uint32_t tmAN = tbase + (16u << 16), tmGV = tbase + (16u << 16) + 64, tmAD = tbase + (16u << 16) + 128;
     const uint32_t cb = 8 * n0;  // first accumulator column of this thread's fragment
 
     auto issue_loads = [&](int c) {
@@ -204,38 +221,47 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     if (tid == 0) issue_loads(nchunks - 1);
 
     constexpr uint32_t idKK = umma_idesc_bf16(64, 64, false, false);
-    constexpr uint32_t idKK16 = umma_idesc_bf16(64, 16, false, false);
+    constexpr uint32_t idKK96 = umma_idesc_bf16(64, 96, false, false);
     constexpr uint32_t idKM = umma_idesc_bf16(64, 64, false, true);
     constexpr uint32_t idMM = umma_idesc_bf16(64, 64, true, true);
-    const int goff[4] = {0, 0, 48, 80};  // first row of the distance-d copies inside sKD / sRD
+    constexpr int goff[4] = {0, 0, 48, 80};  // first row of the distance-d copies inside sKD / sRD
+    // operand descriptors; a step of 16 along K is +2 (K-major operand) or +128 (MN-major operand)
+    const uint64_t dR = umma_desc_sw128(smem_u32(sR)), dK = umma_desc_sw128(smem_u32(sK));
+    const uint64_t dV = umma_desc_sw128(smem_u32(sV)), dW = umma_desc_sw128(smem_u32(sW));
+    const uint64_t dG = umma_desc_sw128(smem_u32(sG)), dS = umma_desc_sw128(smem_u32(sS));
+    const uint64_t dKH = umma_desc_sw128(smem_u32(sKH)), dKD = umma_desc_sw128(smem_u32(sKD));
+    const uint64_t dRD = umma_desc_sw128(smem_u32(sRD)), dP = umma_desc_sw128(smem_u32(sP));
+    const uint64_t dAM = umma_desc_sw128(smem_u32(sAM)), dAB = umma_desc_sw128(smem_u32(sAB));
 
     int err = 0;
     bool load_pending = true;  // thread 0
     for (int it = 0; it < nchunks; ++it) {
         const int c = nchunks - 1 - it;
         WKV6_TSTAMP(it, 0);
-        if (!mbar_wait(bar_full, it & 1)) err = 1;
+        if (!cta_wait(bar_full, it & 1, warp)) err = 1;
         if (tid == 0) load_pending = false;
         WKV6_TSTAMP(it, 1);
 
         // ---- per-step log2 decays and their running sums inside the block (fragment layout)
-        uint32_t rp[8], kp[8];  // raw r, k as packed bf16 pairs: index 2*nn + (0: row ta, 1: row ta+8)
+        __nv_bfloat162 rp[8], kp[8];  // raw r, k pairs: index 2*nn + (row ta+8 ? 1 : 0)
+        __nv_bfloat162 erb[8], ekb[8], lwb[8];  // e^{c_{t-1}-ref}, e^{ref-c_t}, log2-decay, rounded to bf16
         float cs[16], lw[16];
+        const bool full_chunk = (c + 1) * kChunk <= a.T;
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn) {
-            const int col = 8 * (n0 + nn) + 2 * q;
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
-                const int t = ta + 8 * hrow;
-                const uint32_t off = sw128_off(t, col);
-                rp[2 * nn + hrow] = *reinterpret_cast<const uint32_t *>(sR + off);
-                kp[2 * nn + hrow] = *reinterpret_cast<const uint32_t *>(sK + off);
-                const float2 w2 = ld_bf2(sW + off);
-                float lx = fmaxf(-ex2f(w2.x * kLog2e) * kLog2e, kMinLogDecay2);
-                float ly = fmaxf(-ex2f(w2.y * kLog2e) * kLog2e, kMinLogDecay2);
-                if (c * kChunk + t >= a.T) { lx = 0.f; ly = 0.f; }
-                lw[4 * nn + 2 * hrow] = lx;
-                lw[4 * nn + 2 * hrow + 1] = ly;
+                const uint32_t off = fo[2 * nn + hrow];
+                rp[2 * nn + hrow] = *reinterpret_cast<const __nv_bfloat162 *>(sR + off);
+                kp[2 * nn + hrow] = *reinterpret_cast<const __nv_bfloat162 *>(sK + off);
+                const float2 e2 = mul2(ld_bf2(sW + off), make_float2(kLog2e, kLog2e));
+                float2 l2 = mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
+                l2.x = fmaxf(l2.x, kMinLogDecay2);
+                l2.y = fmaxf(l2.y, kMinLogDecay2);
+                if (!full_chunk && c * kChunk + ta + 8 * hrow >= a.T) l2 = make_float2(0.f, 0.f);
+                lw[4 * nn + 2 * hrow] = l2.x;
+                lw[4 * nn + 2 * hrow + 1] = l2.y;
+                lwb[2 * nn + hrow] = to_bf2(l2);
             }
         }
 #pragma unroll
@@ -263,23 +289,23 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         // ---- per (block, channel) factors, one pair per thread
         {
             const int J = tid >> 6, i = tid & 63;
-            float base = 0.f, mybase = 0.f, myref = 0.f, all = 0.f;
+            float base = 0.f, mybase = 0.f, myref = 0.f;
 #pragma unroll
             for (int J2 = 0; J2 < 4; ++J2) {
                 const float rf = rintf(base + sHead[J2 * 64 + i]);  // integer: block-pair factors become powers of two
                 if (J2 == J) { mybase = base; myref = rf; }
                 base += sTot[J2 * 64 + i];
             }
-            all = base;
             sRef[J * 64 + i] = myref;
             sOff[J * 64 + i] = myref - mybase;
-            sFK[J * 64 + i] = ex2f(all - myref);
-            if (J == 0) sDtot[i] = ex2f(all);
+            sFK[J * 64 + i] = ex2f(base - myref);
+            if (J == 0) sDtot[i] = ex2f(base);
         }
         __syncthreads();
         WKV6_TSTAMP(it, 3);
 
-        // ---- scaled operands
+        // ---- scaled operands, on packed bf16 pairs (r, k are exact bf16; the factors are rounded to bf16, the
+        // block-pair and chunk-start factors are powers of two and stay exact)
         {
             float bon_a = 0.f, bon_b = 0.f;
 #pragma unroll
@@ -287,44 +313,46 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 const int col = 8 * (n0 + nn) + 2 * q;
                 const float2 of = *reinterpret_cast<const float2 *>(&sOff[w4 * 64 + col]);
                 const float2 rf = *reinterpret_cast<const float2 *>(&sRef[w4 * 64 + col]);
-                const float2 fk = *reinterpret_cast<const float2 *>(&sFK[w4 * 64 + col]);
-                const float2 fr = make_float2(pow2i(rf.x), pow2i(rf.y));
-                float2 mk[3], mr[3];  // power-of-two factors of the copies for block distances 1..3
+                const __nv_bfloat162 fkb = to_bf2(*reinterpret_cast<const float2 *>(&sFK[w4 * 64 + col]));
+                const __nv_bfloat162 frb = to_bf2(make_float2(pow2i(rf.x), pow2i(rf.y)));
+                __nv_bfloat162 mk[3], mr[3];  // power-of-two factors of the copies for block distances 1..3
 #pragma unroll
                 for (int d = 1; d <= 3; ++d) {
-                    mk[d - 1] = mr[d - 1] = make_float2(0.f, 0.f);
+                    mk[d - 1] = mr[d - 1] = to_bf2(make_float2(0.f, 0.f));
                     if (w4 + d <= 3) {
                         const float2 rt2 = *reinterpret_cast<const float2 *>(&sRef[(w4 + d) * 64 + col]);
-                        mk[d - 1] = make_float2(pow2i(rt2.x - rf.x), pow2i(rt2.y - rf.y));
+                        mk[d - 1] = to_bf2(make_float2(pow2i(rt2.x - rf.x), pow2i(rt2.y - rf.y)));
                     }
                     if (w4 - d >= 0) {
                         const float2 rs2 = *reinterpret_cast<const float2 *>(&sRef[(w4 - d) * 64 + col]);
-                        mr[d - 1] = make_float2(pow2i(rf.x - rs2.x), pow2i(rf.y - rs2.y));
+                        mr[d - 1] = to_bf2(make_float2(pow2i(rf.x - rs2.x), pow2i(rf.y - rs2.y)));
                     }
                 }
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int t = ta + 8 * hrow;
-                    const uint32_t off = sw128_off(t, col);
+                    const uint32_t off = fo[2 * nn + hrow];
                     const int e0 = 4 * nn + 2 * hrow;
-                    const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&rp[2 * nn + hrow]));
-                    const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kp[2 * nn + hrow]));
-                    const float erx = ex2f(cs[e0] - lw[e0] - of.x), ery = ex2f(cs[e0 + 1] - lw[e0 + 1] - of.y);
-                    const float ekx = ex2f(of.x - cs[e0]), eky = ex2f(of.y - cs[e0 + 1]);
-                    const float rtx = __fmul_rn(r2.x, erx), rty = __fmul_rn(r2.y, ery);
-                    const float ktx = __fmul_rn(k2.x, ekx), kty = __fmul_rn(k2.y, eky);
-                    const float bon = r2.x * u_c[2 * nn] * k2.x + r2.y * u_c[2 * nn + 1] * k2.y;
+                    const float2 ea = make_float2(cs[e0] - lw[e0] - of.x, cs[e0 + 1] - lw[e0 + 1] - of.y);
+                    const float2 eb = make_float2(of.x - cs[e0], of.y - cs[e0 + 1]);
+                    const __nv_bfloat162 er = to_bf2(make_float2(ex2f(ea.x), ex2f(ea.y)));
+                    const __nv_bfloat162 ek = to_bf2(make_float2(ex2f(eb.x), ex2f(eb.y)));
+                    erb[2 * nn + hrow] = er;
+                    ekb[2 * nn + hrow] = ek;
+                    const __nv_bfloat162 rb = rp[2 * nn + hrow], kb = kp[2 * nn + hrow];
+                    const float2 rk = mul2(__bfloat1622float2(rb), __bfloat1622float2(kb));
+                    const float bon = fmaf(rk.x, u_c[nn].x, rk.y * u_c[nn].y);
                     if (hrow == 0) bon_a += bon; else bon_b += bon;
-                    st_bf2(sR + off, rtx, rty);
-                    st_bf2(sW + off, rtx * fr.x, rty * fr.y);
-                    st_bf2(sK + off, ktx, kty);
-                    st_bf2(sKH + off, ktx * fk.x, kty * fk.y);
+                    const __nv_bfloat162 rt = __hmul2(rb, er), kt = __hmul2(kb, ek);
+                    *reinterpret_cast<__nv_bfloat162 *>(sR + off) = rt;
+                    *reinterpret_cast<__nv_bfloat162 *>(sW + off) = __hmul2(rt, frb);
+                    *reinterpret_cast<__nv_bfloat162 *>(sK + off) = kt;
+                    *reinterpret_cast<__nv_bfloat162 *>(sKH + off) = __hmul2(kt, fkb);
 #pragma unroll
                     for (int d = 1; d <= 3; ++d) {
-                        if (w4 + d <= 3)  // k~ copy serving row block w4 + d
-                            st_bf2(sKD + sw128_off(goff[d] + t, col), ktx * mk[d - 1].x, kty * mk[d - 1].y);
-                        if (w4 - d >= 0)  // r~ copy serving column block w4 - d
-                            st_bf2(sRD + sw128_off(goff[d] + t - 16 * d, col), rtx * mr[d - 1].x, rty * mr[d - 1].y);
+                        if (w4 + d <= 3)  // k~ copy serving row block w4 + d: row goff[d] + t
+                            *reinterpret_cast<__nv_bfloat162 *>(sKD + goff[d] * 128 + off) = __hmul2(kt, mk[d - 1]);
+                        if (w4 - d >= 0)  // r~ copy serving column block w4 - d: row goff[d] + t - 16 d
+                            *reinterpret_cast<__nv_bfloat162 *>(sRD + (goff[d] - 16 * d) * 128 + off) = __hmul2(rt, mr[d - 1]);
                     }
                 }
             }
@@ -337,41 +365,39 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         __syncthreads();
         WKV6_TSTAMP(it, 4);
 
-        // ---- MMA group 1
-        if (tid == 0) {
+        // ---- MMA group 1, four issuing threads (independent accumulators)
+        if (lane == 0 && warp < 4) {
             tc_fence_after_sync();
-            const uint32_t aR = smem_u32(sR), aK = smem_u32(sK), aV = smem_u32(sV), aW = smem_u32(sW), aG = smem_u32(sG);
-            const uint32_t aS = smem_u32(sS), aKH = smem_u32(sKH), aKD = smem_u32(sKD), aAB = smem_u32(sAB);
+            if (warp == 0) {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // P = gy v^T
-                umma_ss(tmP, umma_desc_sw128(aG + 32 * kk), umma_desc_sw128(aV + 32 * kk), idKK, kk > 0);
+                for (int kk = 0; kk < 4; ++kk)  // P = gy v^T
+                    umma_ss(tmP, dG + 2 * kk, dV + 2 * kk, idKK, kk > 0);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // A, distance-0 copies everywhere (valid on the diagonal blocks)
-                umma_ss(tmA, umma_desc_sw128(aR + 32 * kk), umma_desc_sw128(aK + 32 * kk), idKK, kk > 0);
+                for (int kk = 0; kk < 4; ++kk)  // GR2 = gy S_in^T
+                    umma_ss(tmGR2, dG + 2 * kk, dS + 2 * kk, idKK, kk > 0);
+            } else if (warp == 1) {
 #pragma unroll
-            for (int I = 1; I < 4; ++I)
+                for (int kk = 0; kk < 4; ++kk)  // A, distance 0
+                    umma_ss(tmA, dR + 2 * kk, dK + 2 * kk, idKK, kk > 0);
 #pragma unroll
-                for (int J = 0; J < I; ++J)  // A block (I, J) from the distance-(I-J) copy of k~_J
+                for (int kk = 0; kk < 4; ++kk)  // A, distances 1..3: r~ against the 96 rows of k~ copies
+                    umma_ss(tmAD, dR + 2 * kk, dKD + 2 * kk, idKK96, kk > 0);
+            } else if (warp == 2) {
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_ss_masked(tmA + 16 * J, umma_desc_sw128(aR + 32 * kk),
-                                       umma_desc_sw128(aKD + (goff[I - J] + 16 * J) * 128 + 32 * kk), idKK16, kk > 0, I);
+                for (int kk = 0; kk < 4; ++kk)  // GK2 = v Abar^T
+                    umma_ss(tmGK2, dV + 2 * kk, dAB + 2 * kk, idKK, kk > 0);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // GR2 = gy S_in^T
-                umma_ss(tmGR2, umma_desc_sw128(aG + 32 * kk), umma_desc_sw128(aS + 32 * kk), idKK, kk > 0);
+                for (int kk = 0; kk < 4; ++kk)  // gv = k^ Abar
+                    umma_ss(tmGV, dKH + 2 * kk, dAB + 128 * kk, idKM, kk > 0);
+            } else {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // GK2 = v Abar^T
-                umma_ss(tmGK2, umma_desc_sw128(aV + 32 * kk), umma_desc_sw128(aAB + 32 * kk), idKK, kk > 0);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // Abar increment = r^^T gy
-                umma_ss(tmAN, umma_desc_sw128(aW + 2048 * kk), umma_desc_sw128(aG + 2048 * kk), idMM, kk > 0);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // gv = k^ Abar
-                umma_ss(tmGV, umma_desc_sw128(aKH + 32 * kk), umma_desc_sw128(aAB + 2048 * kk), idKM, kk > 0);
+                for (int kk = 0; kk < 4; ++kk)  // Abar increment = r^^T gy
+                    umma_ss(tmAN, dW + 128 * kk, dG + 128 * kk, idMM, kk > 0);
+            }
             umma_commit(bar_mma1);
         }
         WKV6_TSTAMP(it, 5);
-        if (!mbar_wait(bar_mma1, it & 1)) err = 2;
+        if (!cta_wait(bar_mma1, it & 1, warp)) err = 2;
         tc_fence_after_sync();
         WKV6_TSTAMP(it, 6);
 
@@ -390,29 +416,44 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                     if (s0 + 1 == t) sVG[t] = x1;
                     x0 = (s0 < t) ? x0 : 0.f;
                     x1 = (s0 + 1 < t) ? x1 : 0.f;
-                    *reinterpret_cast<uint32_t *>(sP + sw128_off(t, s0)) = pack_bf2(x0, x1);
+                    *reinterpret_cast<uint32_t *>(sP + fo[2 * nn + hrow]) = pack_bf2(x0, x1);
                 }
             }
-            tmem_ld_16x256b_x4(tmA + lo + cb, f);
+            // A: this warp covers column blocks J = 2*half, 2*half+1 of row block I = w4; pick the copy per block pair
 #pragma unroll
-            for (int nn = 0; nn < 4; ++nn) {
-                const int s0 = 8 * (n0 + nn) + 2 * q;
+            for (int jj = 0; jj < 2; ++jj) {
+                const int J = 2 * half + jj, I = w4;
+                uint32_t o0 = 0, o1 = 0, o2 = 0, o3 = 0;
+                if (J <= I) {
+                    const int dl = I - J;
+                    const uint32_t src = (dl == 0) ? (tmA + lo + 16 * J) : (tmAD + lo + goff[dl] + 16 * J);
+                    uint32_t v8[8];
+                    tmem_ld_16x256b_x2(src, v8);
+                    tmem_wait_ld();
+                    float g8[8];
 #pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int t = ta + 8 * hrow;
-                    float x0 = f[4 * nn + 2 * hrow], x1 = f[4 * nn + 2 * hrow + 1];
-                    const float bonus = sBonus[t] + sBonus[64 + t];
-                    x0 = (s0 < t) ? x0 : (s0 == t ? bonus : 0.f);
-                    x1 = (s0 + 1 < t) ? x1 : (s0 + 1 == t ? bonus : 0.f);
-                    *reinterpret_cast<uint32_t *>(sAM + sw128_off(t, s0)) = pack_bf2(x0, x1);
+                    for (int e = 0; e < 8; ++e) g8[e] = __uint_as_float(v8[e]);
+                    if (dl == 0) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int row = r0 + ((e & 2) ? 8 : 0);
+                            const int col = 8 * (e >> 2) + 2 * q + (e & 1);
+                            g8[e] = (col < row) ? g8[e] : (col == row ? sBonus[16 * I + row] + sBonus[64 + 16 * I + row] : 0.f);
+                        }
+                    }
+                    o0 = pack_bf2(g8[0], g8[1]); o2 = pack_bf2(g8[2], g8[3]);
+                    o1 = pack_bf2(g8[4], g8[5]); o3 = pack_bf2(g8[6], g8[7]);
                 }
+                *reinterpret_cast<uint32_t *>(sAM + fo[4 * jj]) = o0;
+                *reinterpret_cast<uint32_t *>(sAM + fo[4 * jj + 2]) = o1;
+                *reinterpret_cast<uint32_t *>(sAM + fo[4 * jj + 1]) = o2;
+                *reinterpret_cast<uint32_t *>(sAM + fo[4 * jj + 3]) = o3;
             }
             // <S_in, Abar>_i with the reverse state at the chunk end (before its update), for gw
             float za = 0.f, zb = 0.f;
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
-                const int j0 = 8 * (n0 + nn) + 2 * q;
-                const float2 sa = ld_bf2(sS + sw128_off(ta, j0)), sb = ld_bf2(sS + sw128_off(ta + 8, j0));
+                const float2 sa = ld_bf2(sS + fo[2 * nn]), sb = ld_bf2(sS + fo[2 * nn + 1]);
                 za = fmaf(AB[4 * nn], sa.x, fmaf(AB[4 * nn + 1], sa.y, za));
                 zb = fmaf(AB[4 * nn + 2], sb.x, fmaf(AB[4 * nn + 3], sb.y, zb));
             }
@@ -426,13 +467,12 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
             const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
-                const int j0 = 8 * (n0 + nn) + 2 * q;
                 AB[4 * nn + 0] = fmaf(AB[4 * nn + 0], d0, f[4 * nn + 0]);
                 AB[4 * nn + 1] = fmaf(AB[4 * nn + 1], d0, f[4 * nn + 1]);
                 AB[4 * nn + 2] = fmaf(AB[4 * nn + 2], d1, f[4 * nn + 2]);
                 AB[4 * nn + 3] = fmaf(AB[4 * nn + 3], d1, f[4 * nn + 3]);
-                *reinterpret_cast<uint32_t *>(sAB + sw128_off(ta, j0)) = pack_bf2(AB[4 * nn], AB[4 * nn + 1]);
-                *reinterpret_cast<uint32_t *>(sAB + sw128_off(ta + 8, j0)) = pack_bf2(AB[4 * nn + 2], AB[4 * nn + 3]);
+                *reinterpret_cast<uint32_t *>(sAB + fo[2 * nn]) = pack_bf2(AB[4 * nn], AB[4 * nn + 1]);
+                *reinterpret_cast<uint32_t *>(sAB + fo[2 * nn + 1]) = pack_bf2(AB[4 * nn + 2], AB[4 * nn + 3]);
             }
         }
         fence_proxy_async_smem();
@@ -440,158 +480,133 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         if (!__syncthreads_and(err == 0)) { err = err ? err : 11; break; }
         WKV6_TSTAMP(it, 7);
 
-        // ---- MMA group 2
-        if (tid == 0) {
+        // ---- MMA group 2, three issuing threads
+        if (lane == 0 && warp < 3) {
             tc_fence_after_sync();
-            const uint32_t aR = smem_u32(sR), aK = smem_u32(sK), aG = smem_u32(sG), aP = smem_u32(sP);
-            const uint32_t aKD = smem_u32(sKD), aRD = smem_u32(sRD), aAM = smem_u32(sAM);
+            if (warp == 0) {
 #pragma unroll
-            for (int I = 0; I < 4; ++I)
+                for (int I = 0; I < 4; ++I)
 #pragma unroll
-                for (int J = 0; J <= I; ++J) {
-                    // GR1 rows of block I += P[:, block J] k~copy(I-J)_J        (K = the 16 tokens of block J)
-                    const uint32_t kb = (I == J) ? aK + 2048 * J : aKD + (goff[I - J] + 16 * J) * 128;
-                    umma_ss_masked(tmP, umma_desc_sw128(aP + 32 * J), umma_desc_sw128(kb), idKM, J > 0, I);
-                }
+                    for (int J = 0; J <= I; ++J) {
+                        // GR1 rows of block I += P[:, block J] k~copy(I-J)_J        (K = the 16 tokens of block J)
+                        const uint64_t kb = (I == J) ? dK + 128 * J : dKD + 8 * (goff[I - J] + 16 * J);
+                        umma_ss_masked(tmP, dP + 2 * J, kb, idKM, J > 0, I);
+                    }
+            } else if (warp == 1) {
 #pragma unroll
-            for (int J = 0; J < 4; ++J)
+                for (int J = 0; J < 4; ++J)
 #pragma unroll
-                for (int I = J; I < 4; ++I) {
-                    // GK1 rows of block J += P[block I, :]^T r~copy(I-J)_I      (K = the 16 tokens of block I)
-                    const uint32_t rb = (I == J) ? aR + 2048 * I : aRD + (goff[I - J] + 16 * J) * 128;
-                    umma_ss_masked(tmA, umma_desc_sw128(aP + 2048 * I), umma_desc_sw128(rb), idMM, I > J, J);
-                }
+                    for (int I = J; I < 4; ++I) {
+                        // GK1 rows of block J += P[block I, :]^T r~copy(I-J)_I      (K = the 16 tokens of block I)
+                        const uint64_t rb2 = (I == J) ? dR + 128 * I : dRD + 8 * (goff[I - J] + 16 * J);
+                        umma_ss_masked(tmA, dP + 128 * I, rb2, idMM, I > J, J);
+                    }
+            } else {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // gv += A^T gy
-                umma_ss(tmGV, umma_desc_sw128(aAM + 2048 * kk), umma_desc_sw128(aG + 2048 * kk), idMM, true);
+                for (int kk = 0; kk < 4; ++kk)  // gv += A^T gy
+                    umma_ss(tmGV, dAM + 128 * kk, dG + 128 * kk, idMM, true);
+            }
             umma_commit(bar_mma2);
         }
         WKV6_TSTAMP(it, 8);
-        if (!mbar_wait(bar_mma2, it & 1)) err = 3;
+        if (!cta_wait(bar_mma2, it & 1, warp)) err = 3;
         tc_fence_after_sync();
         WKV6_TSTAMP(it, 9);
         // every input tile is dead once the second MMA group has completed: fetch the next chunk now
         if (tid == 0 && c > 0 && err == 0) { issue_loads(c - 1); load_pending = true; }
 
-        // ---- epilogue 2: gr, gk, gv, gw
+        // ---- epilogue 2: gr, gk, gv, gw, one 8-column repetition at a time
+        float loc[16];  // G minus its per-channel base (see below)
         {
-            float g1[16], g2[16];
-            float qv[16], zb[16];  // qv = a - z - b (see the gw formula above), zb = z + b
             const float vga = sVG[ta], vgb = sVG[ta + 8];
-            tmem_ld_16x256b_x4(tmP + lo + cb, g1);    // GR1
-            tmem_ld_16x256b_x4(tmGR2 + lo + cb, g2);  // GR2
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 const int col = 8 * (n0 + nn) + 2 * q;
-                const float2 of = *reinterpret_cast<const float2 *>(&sOff[w4 * 64 + col]);
+                float g1[4], g2[4], h1[4], h2[4];
+                tmem_ld_16x256b_x1(tmP + lo + cb + 8 * nn, g1);    // GR1
+                tmem_ld_16x256b_x1(tmGR2 + lo + cb + 8 * nn, g2);  // GR2
+                tmem_ld_16x256b_x1(tmA + lo + cb + 8 * nn, h1);    // GK1
+                tmem_ld_16x256b_x1(tmGK2 + lo + cb + 8 * nn, h2);  // GK2
+                tmem_wait_ld();
                 const float2 rf = *reinterpret_cast<const float2 *>(&sRef[w4 * 64 + col]);
                 const float2 fr = make_float2(pow2i(rf.x), pow2i(rf.y));
-#pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int e0 = 4 * nn + 2 * hrow;
-                    const float vg = hrow ? vgb : vga;
-                    const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&rp[2 * nn + hrow]));
-                    const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kp[2 * nn + hrow]));
-                    const float erx = ex2f(cs[e0] - lw[e0] - of.x), ery = ex2f(cs[e0 + 1] - lw[e0 + 1] - of.y);
-                    const float rtx = __fmul_rn(r2.x, erx), rty = __fmul_rn(r2.y, ery);  // as in the operand pass
-                    const float rbx = __bfloat162float(__float2bfloat16_rn(rtx)), rby = __bfloat162float(__float2bfloat16_rn(rty));
-                    const float grx = fmaf(erx, fmaf(fr.x, g2[e0], g1[e0]), u_c[2 * nn] * k2.x * vg);
-                    const float gry = fmaf(ery, fmaf(fr.y, g2[e0 + 1], g1[e0 + 1]), u_c[2 * nn + 1] * k2.y * vg);
-                    qv[e0] = fmaf(rbx, g1[e0], (rtx * fr.x) * g2[e0]);
-                    qv[e0 + 1] = fmaf(rby, g1[e0 + 1], (rty * fr.y) * g2[e0 + 1]);
-                    *reinterpret_cast<uint32_t *>(sP + sw128_off(ta + 8 * hrow, col)) = pack_bf2(grx, gry);
-                }
-            }
-            tmem_ld_16x256b_x4(tmA + lo + cb, g1);    // GK1
-            tmem_ld_16x256b_x4(tmGK2 + lo + cb, g2);  // GK2
-            float bsum[8];
-#pragma unroll
-            for (int nn = 0; nn < 4; ++nn) {
-                const int col = 8 * (n0 + nn) + 2 * q;
-                const float2 of = *reinterpret_cast<const float2 *>(&sOff[w4 * 64 + col]);
                 const float2 fk = *reinterpret_cast<const float2 *>(&sFK[w4 * 64 + col]);
-                bsum[2 * nn] = 0.f; bsum[2 * nn + 1] = 0.f;
+                float qv[4], bsum0 = 0.f, bsum1 = 0.f;
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int e0 = 4 * nn + 2 * hrow;
                     const float vg = hrow ? vgb : vga;
-                    const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&rp[2 * nn + hrow]));
-                    const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&kp[2 * nn + hrow]));
-                    const float ekx = ex2f(of.x - cs[e0]), eky = ex2f(of.y - cs[e0 + 1]);
-                    const float ktx = __fmul_rn(k2.x, ekx), kty = __fmul_rn(k2.y, eky);
-                    const float kbx = __bfloat162float(__float2bfloat16_rn(ktx)), kby = __bfloat162float(__float2bfloat16_rn(kty));
-                    const float gkx = fmaf(ekx, fmaf(fk.x, g2[e0], g1[e0]), u_c[2 * nn] * r2.x * vg);
-                    const float gky = fmaf(eky, fmaf(fk.y, g2[e0 + 1], g1[e0 + 1]), u_c[2 * nn + 1] * r2.y * vg);
-                    const float zx = kbx * g1[e0], zy = kby * g1[e0 + 1];
-                    const float bx = (ktx * fk.x) * g2[e0], by = (kty * fk.y) * g2[e0 + 1];
-                    zb[e0] = zx + bx; zb[e0 + 1] = zy + by;
-                    qv[e0] -= zb[e0]; qv[e0 + 1] -= zb[e0 + 1];
-                    bsum[2 * nn] += bx; bsum[2 * nn + 1] += by;
-                    gu_acc[2 * nn] = fmaf(r2.x * k2.x, vg, gu_acc[2 * nn]);
-                    gu_acc[2 * nn + 1] = fmaf(r2.y * k2.y, vg, gu_acc[2 * nn + 1]);
-                    *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta + 8 * hrow, col)) = pack_bf2(gkx, gky);
+                    const float2 r2 = __bfloat1622float2(rp[2 * nn + hrow]), k2 = __bfloat1622float2(kp[2 * nn + hrow]);
+                    const float2 er = __bfloat1622float2(erb[2 * nn + hrow]), ek = __bfloat1622float2(ekb[2 * nn + hrow]);
+                    // the bf16 operand values r~, k~ exactly as the MMAs saw them
+                    const float2 rt = __bfloat1622float2(__hmul2(rp[2 * nn + hrow], erb[2 * nn + hrow]));
+                    const float2 kt = __bfloat1622float2(__hmul2(kp[2 * nn + hrow], ekb[2 * nn + hrow]));
+                    const float2 G1 = make_float2(g1[2 * hrow], g1[2 * hrow + 1]), G2 = make_float2(g2[2 * hrow], g2[2 * hrow + 1]);
+                    const float2 H1 = make_float2(h1[2 * hrow], h1[2 * hrow + 1]), H2 = make_float2(h2[2 * hrow], h2[2 * hrow + 1]);
+                    const float2 uvg = make_float2(u_c[nn].x * vg, u_c[nn].y * vg);
+                    // gr = Er (GR1 + fR GR2) + u k vg ;  gk = Ek (GK1 + fK GK2) + u r vg
+                    const float2 gr = fma2(er, fma2(fr, G2, G1), mul2(uvg, k2));
+                    const float2 gk = fma2(ek, fma2(fk, H2, H1), mul2(uvg, r2));
+                    *reinterpret_cast<__nv_bfloat162 *>(sP + fo[2 * nn + hrow]) = to_bf2(gr);
+                    *reinterpret_cast<__nv_bfloat162 *>(sAM + fo[2 * nn + hrow]) = to_bf2(gk);
+                    // gw pieces: a = r~ GR1 + r^ GR2, z = k~ GK1, b = k^ GK2
+                    const float2 av = fma2(rt, G1, mul2(mul2(rt, fr), G2));
+                    const float2 zv = mul2(kt, H1);
+                    const float2 bv = mul2(mul2(kt, fk), H2);
+                    const float2 zbv = add2(zv, bv);
+                    qv[2 * hrow] = av.x - zbv.x;
+                    qv[2 * hrow + 1] = av.y - zbv.y;
+                    loc[4 * nn + 2 * hrow] = -av.x;      // becomes  suffix_incl(q) - q - (z + b) = suffix_incl(q) - a
+                    loc[4 * nn + 2 * hrow + 1] = -av.y;
+                    bsum0 += bv.x; bsum1 += bv.y;
+                    const float2 rkv = mul2(mul2(r2, k2), make_float2(vg, vg));
+                    gu_acc[2 * nn] += rkv.x;
+                    gu_acc[2 * nn + 1] += rkv.y;
                 }
-            }
-            tmem_ld_16x256b_x4(tmGV + lo + cb, g1);
-#pragma unroll
-            for (int nn = 0; nn < 4; ++nn) {
-                const int col = 8 * (n0 + nn) + 2 * q;
-                *reinterpret_cast<uint32_t *>(sKD + sw128_off(ta, col)) = pack_bf2(g1[4 * nn], g1[4 * nn + 1]);
-                *reinterpret_cast<uint32_t *>(sKD + sw128_off(ta + 8, col)) = pack_bf2(g1[4 * nn + 2], g1[4 * nn + 3]);
-            }
-            // sums over later tokens: inside the block by lane scans, across blocks through shared memory
-            float incl[16];
-#pragma unroll
-            for (int nn = 0; nn < 4; ++nn)
+                // sums over later tokens of the block by lane scans; block totals go through shared memory
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    float pa = qv[4 * nn + e], pb = qv[4 * nn + 2 + e];
+                    float pa = qv[e], pb = qv[2 + e];
                     scan_suffix16(pa, pb, r0, lane);
-                    incl[4 * nn + e] = pa;
-                    incl[4 * nn + 2 + e] = pb;
-                    float bs = bsum[2 * nn + e];
-                    bs += __shfl_xor_sync(0xffffffffu, bs, 4);
-                    bs += __shfl_xor_sync(0xffffffffu, bs, 8);
-                    bs += __shfl_xor_sync(0xffffffffu, bs, 16);
-                    bsum[2 * nn + e] = bs;
+                    loc[4 * nn + e] += pa;
+                    loc[4 * nn + 2 + e] += pb;
+                    if (r0 == 0) sXtot[w4 * 64 + col + e] = pa;
                 }
-            if (r0 == 0) {
-#pragma unroll
-                for (int nn = 0; nn < 4; ++nn) {
-                    const int col = 8 * (n0 + nn) + 2 * q;
-                    *reinterpret_cast<float2 *>(&sXtot[w4 * 64 + col]) = make_float2(incl[4 * nn], incl[4 * nn + 1]);
-                    *reinterpret_cast<float2 *>(&sBtot[w4 * 64 + col]) = make_float2(bsum[2 * nn], bsum[2 * nn + 1]);
-                }
+                bsum0 += __shfl_xor_sync(0xffffffffu, bsum0, 4); bsum1 += __shfl_xor_sync(0xffffffffu, bsum1, 4);
+                bsum0 += __shfl_xor_sync(0xffffffffu, bsum0, 8); bsum1 += __shfl_xor_sync(0xffffffffu, bsum1, 8);
+                bsum0 += __shfl_xor_sync(0xffffffffu, bsum0, 16); bsum1 += __shfl_xor_sync(0xffffffffu, bsum1, 16);
+                if (r0 == 0) *reinterpret_cast<float2 *>(&sBtot[w4 * 64 + col]) = make_float2(bsum0, bsum1);
             }
-            tc_fence_before_sync();
-            __syncthreads();
-            WKV6_TSTAMP(it, 10);
+            float gv16[16];
+            tmem_ld_16x256b_x4(tmGV + lo + cb, gv16);
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
-                const int col = 8 * (n0 + nn) + 2 * q;
-                const float2 t1 = *reinterpret_cast<const float2 *>(&sT1[col]);
-                const float2 dt = *reinterpret_cast<const float2 *>(&sDtot[col]);
-                float2 base = make_float2(t1.x * dt.x, t1.y * dt.y);
+                *reinterpret_cast<uint32_t *>(sKD + fo[2 * nn]) = pack_bf2(gv16[4 * nn], gv16[4 * nn + 1]);
+                *reinterpret_cast<uint32_t *>(sKD + fo[2 * nn + 1]) = pack_bf2(gv16[4 * nn + 2], gv16[4 * nn + 3]);
+            }
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        WKV6_TSTAMP(it, 10);
+        // G_t = e^{c_63} <S_in, Abar> + sum_all b + sum_{later blocks} q + (suffix_incl(q) - a)_t ;  gw = -exp(w) G
 #pragma unroll
-                for (int J2 = 0; J2 < 4; ++J2) {
-                    const float2 bt = *reinterpret_cast<const float2 *>(&sBtot[J2 * 64 + col]);
-                    base.x += bt.x; base.y += bt.y;
-                    if (J2 > w4) {
-                        const float2 xt = *reinterpret_cast<const float2 *>(&sXtot[J2 * 64 + col]);
-                        base.x += xt.x; base.y += xt.y;
-                    }
-                }
+        for (int nn = 0; nn < 4; ++nn) {
+            const int col = 8 * (n0 + nn) + 2 * q;
+            const float2 t1 = *reinterpret_cast<const float2 *>(&sT1[col]);
+            const float2 dt = *reinterpret_cast<const float2 *>(&sDtot[col]);
+            float2 base = mul2(t1, dt);
 #pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int e0 = 4 * nn + 2 * hrow;
-                    const int t = ta + 8 * hrow;
-                    const float gx = base.x + (incl[e0] - qv[e0]) - zb[e0];
-                    const float gy2 = base.y + (incl[e0 + 1] - qv[e0 + 1]) - zb[e0 + 1];
-                    float gwx = (lw[e0] * (1.0f / kLog2e)) * gx;  // -exp(w) = log-decay
-                    float gwy = (lw[e0 + 1] * (1.0f / kLog2e)) * gy2;
-                    if (c == 0 && t == 0) { gwx = 0.f; gwy = 0.f; }  // zero initial state: exactly no dependence on w_0
-                    *reinterpret_cast<uint32_t *>(sRD + sw128_off(t, col)) = pack_bf2(gwx, gwy);
-                }
+            for (int J2 = 0; J2 < 4; ++J2) {
+                base = add2(base, *reinterpret_cast<const float2 *>(&sBtot[J2 * 64 + col]));
+                if (J2 > w4) base = add2(base, *reinterpret_cast<const float2 *>(&sXtot[J2 * 64 + col]));
+            }
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int e0 = 4 * nn + 2 * hrow;
+                const float2 lwf = __bfloat1622float2(lwb[2 * nn + hrow]);
+                float2 gw = mul2(mul2(lwf, make_float2(1.0f / kLog2e, 1.0f / kLog2e)),
+                                 make_float2(base.x + loc[e0], base.y + loc[e0 + 1]));  // -exp(w) = log-decay
+                if (c == 0 && ta + 8 * hrow == 0) gw = make_float2(0.f, 0.f);  // zero initial state: no dependence on w_0
+                *reinterpret_cast<__nv_bfloat162 *>(sRD + fo[2 * nn + hrow]) = to_bf2(gw);
             }
         }
         fence_proxy_async_smem();
@@ -619,11 +634,11 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     // gu[b][h][i]: sum this thread's channels over the 8 lanes sharing q, then over the four row blocks
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-        float s = gu_acc[e];
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        s += __shfl_xor_sync(0xffffffffu, s, 8);
-        s += __shfl_xor_sync(0xffffffffu, s, 16);
-        gu_acc[e] = s;
+        float s2 = gu_acc[e];
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 4);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 8);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 16);
+        gu_acc[e] = s2;
     }
     __syncthreads();
     if (r0 == 0) {

@@ -59,7 +59,7 @@ struct ChunkFwdSmem {
     static constexpr int oBar = oBonus + 64 * 4;             // mbarriers: full[2], mma1, mma2
     static constexpr int oSlot = oBar + 4 * 8;
     static constexpr int kBytes = oSlot + 16;
-    static constexpr int kAlloc = kBytes + 1024;             // slack for the 1024-byte alignment of the base
+    static constexpr int kAlloc = kBytes;
 };
 
 struct ChunkFwdArgs {
@@ -70,7 +70,11 @@ struct ChunkFwdArgs {
     bool write_y;         // false: only states / checkpoints are produced
 };
 
+#ifndef WKV6_EXP
+#define WKV6_EXP 0  // experiment switches of instrumented builds; 0 in every product build
+#endif
 __device__ __forceinline__ float ex2f(float x) {
+    if (WKV6_EXP & 2) return x * 0.5f + 1.0f;
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
@@ -81,6 +85,36 @@ __device__ __forceinline__ float2 ld_bf2(const uint8_t *p) {
 __device__ __forceinline__ void st_bf2(uint8_t *p, float a, float b) {
     *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(a, b);
 }
+// packed fp32 pairs (one issue slot for two lanes of work on sm_100)
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    unsigned long long ra, rb, rc;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rc) : "l"(ra), "l"(rb));
+    float2 c;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(c.x), "=f"(c.y) : "l"(rc));
+    return c;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long ra, rb, rc;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rc) : "l"(ra), "l"(rb));
+    float2 c;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(c.x), "=f"(c.y) : "l"(rc));
+    return c;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ __nv_bfloat162 to_bf2(float2 a) { return __floats2bfloat162_rn(a.x, a.y); }
 __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&h);
@@ -94,8 +128,14 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                                                            const ChunkFwdArgs a) {
     using namespace ptx;
     using SM = ChunkFwdSmem;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Declared with the alignment the swizzled tiles need, so that the compiler keeps every access in the shared
+    // address space with 32-bit addresses; the base is verified once instead of being realigned by pointer math.
+    extern __shared__ __align__(1024) uint8_t wkv6_chunk_smem[];
+    uint8_t *const smem = wkv6_chunk_smem;
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(&g_chunk_status, 50);
+        return;
+    }
     uint8_t *sKH = smem + SM::oKH, *sKD = smem + SM::oKD, *sAM = smem + SM::oAM, *sSB = smem + SM::oSB;
     float *sHead = reinterpret_cast<float *>(smem + SM::oHead);  // [4][64] log2-decay sum of tokens 0..7 of a block
     float *sTail = reinterpret_cast<float *>(smem + SM::oTot);   // [4][64] log2-decay sum of tokens 8..15 of a block
@@ -162,6 +202,13 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     const uint32_t tmA0 = tb, tmY = tb + 64, tmS = tb + 128, tmAD = tb + (16u << 16);
     const uint32_t wl = (uint32_t)(w4 * 32) << 16;  // this warp's TMEM lane quarter
     const uint32_t cb = 8 * n0;                     // first accumulator column of this thread's fragment
+    // byte offsets of this thread's fragment elements (rows ta / ta+8, column pairs 8(n0+nn)+2q) in a swizzled tile
+    uint32_t foA[4], foB[4];
+#pragma unroll
+    for (int nn = 0; nn < 4; ++nn) {
+        foA[nn] = sw128_off(ta, 8 * (n0 + nn) + 2 * q);
+        foB[nn] = sw128_off(ta + 8, 8 * (n0 + nn) + 2 * q);
+    }
 
     auto issue_loads = [&](int c) {
         const int st = c & 1;
@@ -196,25 +243,32 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     int loads_pending = (nchunks > 1) ? 2 : 1;  // meaningful on thread 0 only
     for (int c = 0; c < nchunks; ++c) {
         const int st = c & 1;
-        uint8_t *sR = smem + st * SM::kStage, *sK = sR + kTile, *sW = sR + 3 * kTile;
+        uint8_t *sR = smem + st * SM::kStage;  // this stage: r, k, v, w tiles at +0, +kTile, +2 kTile, +3 kTile
         const uint64_t so = (uint64_t)(st * (SM::kStage >> 4));
         WKV6_TSTAMP(c, 0);
-        if (!mbar_wait(&bar_full[st], (c >> 1) & 1)) err = 1;
+        if (!cta_wait(&bar_full[st], (c >> 1) & 1, warp)) err = 1;
         if (tid == 0) --loads_pending;
         WKV6_TSTAMP(c, 1);
 
-        // ---- pass 1: per-step log2 decays of this thread's 8 tokens x 2 channels, running sums from the first of them
+        // ---- pass 1: per-step log2 decays of this thread's 8 tokens x 2 channels, running sums from the first of them.
+        // Row t = 16*w4 + 8*half + tt has swizzle phase tt, so one per-thread base pointer plus a per-tt XOR term
+        // addresses every tile (tile offsets are compile-time constants relative to the stage base).
+        uint8_t *const tbase = sR + (16 * w4 + 8 * half) * 128 + ((lane & 3) << 2);
+        const uint32_t lane_chunk = (uint32_t)(lane >> 2);
+        const bool full_chunk = (c + 1) * kChunk <= a.T;
         float2 x[8];
         {
             float2 cs = make_float2(0.f, 0.f);
 #pragma unroll
             for (int tt = 0; tt < 8; ++tt) {
-                const int t = 16 * w4 + 8 * half + tt;
-                const float2 w2 = ld_bf2(sW + sw128_off(t, 2 * lane));
-                float lx = fmaxf(-ex2f(w2.x * kLog2e) * kLog2e, kMinLogDecay2);
-                float ly = fmaxf(-ex2f(w2.y * kLog2e) * kLog2e, kMinLogDecay2);
-                if (c * kChunk + t >= a.T) { lx = 0.f; ly = 0.f; }
-                cs.x += lx; cs.y += ly;
+                const uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
+                const float2 w2 = ld_bf2(pt + 3 * kTile);
+                const float2 e2 = mul2(w2, make_float2(kLog2e, kLog2e));
+                float2 l2 = mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
+                l2.x = fmaxf(l2.x, kMinLogDecay2);
+                l2.y = fmaxf(l2.y, kMinLogDecay2);
+                if (!full_chunk && c * kChunk + 16 * w4 + 8 * half + tt >= a.T) l2 = make_float2(0.f, 0.f);
+                cs = add2(cs, l2);
                 x[tt] = cs;
             }
             *reinterpret_cast<float2 *>(&(half ? sTail : sHead)[w4 * 64 + 2 * lane]) = cs;
@@ -226,6 +280,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
 
         // ---- pass 2: scaled operands.  The block reference is the boundary between the two token halves, so the
         // running sums of the second half are already relative to it and those of the first half need only -head.
+        // The scaling itself runs on packed bf16 pairs: r and k are exact bf16 inputs, factors are rounded to bf16.
         {
             float2 pre = make_float2(0.f, 0.f), post = make_float2(0.f, 0.f), head, tail;
             head = tail = make_float2(0.f, 0.f);
@@ -234,26 +289,26 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             for (int J = 0; J < 4; ++J) {
                 headJ[J] = *reinterpret_cast<const float2 *>(&sHead[J * 64 + 2 * lane]);
                 const float2 tl = *reinterpret_cast<const float2 *>(&sTail[J * 64 + 2 * lane]);
-                totJ[J] = make_float2(headJ[J].x + tl.x, headJ[J].y + tl.y);
-                if (J < w4) { pre.x += totJ[J].x; pre.y += totJ[J].y; }
-                if (J > w4) { post.x += totJ[J].x; post.y += totJ[J].y; }
+                totJ[J] = add2(headJ[J], tl);
+                if (J < w4) pre = add2(pre, totJ[J]);
+                if (J > w4) post = add2(post, totJ[J]);
                 if (J == w4) { head = headJ[J]; tail = tl; }
             }
-            const float2 base = half ? make_float2(0.f, 0.f) : head;
-            const float2 fR = make_float2(ex2f(head.x + pre.x), ex2f(head.y + pre.y));
-            const float2 fK = make_float2(ex2f(tail.x + post.x), ex2f(tail.y + post.y));
+            const float2 nbase = half ? make_float2(0.f, 0.f) : make_float2(-head.x, -head.y);
+            const __nv_bfloat162 fR = to_bf2(make_float2(ex2f(head.x + pre.x), ex2f(head.y + pre.y)));
+            const __nv_bfloat162 fK = to_bf2(make_float2(ex2f(tail.x + post.x), ex2f(tail.y + post.y)));
             // factors of the k~ copies for block distances 1..3 (only those with w4 + delta <= 3 exist)
-            float2 fD[3];
+            __nv_bfloat162 fD[3];
             {
                 float2 acc = tail;
 #pragma unroll
                 for (int dl = 1; dl <= 3; ++dl) {
-                    fD[dl - 1] = make_float2(0.f, 0.f);
+                    fD[dl - 1] = to_bf2(make_float2(0.f, 0.f));
 #pragma unroll
                     for (int Jt = 1; Jt < 4; ++Jt) {
                         if (Jt == w4 + dl) {
-                            fD[dl - 1] = make_float2(ex2f(acc.x + headJ[Jt].x), ex2f(acc.y + headJ[Jt].y));
-                            acc.x += totJ[Jt].x; acc.y += totJ[Jt].y;
+                            fD[dl - 1] = to_bf2(make_float2(ex2f(acc.x + headJ[Jt].x), ex2f(acc.y + headJ[Jt].y)));
+                            acc = add2(acc, totJ[Jt]);
                         }
                     }
                 }
@@ -263,36 +318,61 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 *reinterpret_cast<float2 *>(&sDtot[2 * lane]) = make_float2(ex2f(all.x), ex2f(all.y));
             }
             float bon[8];
-            const uint32_t csw = (uint32_t)(2 * lane);  // channel offset before swizzling
+            const int kdo = (int)(sKD - sR), kho = (int)(sKH - sR);  // uniform offsets of the copy tiles from this stage
+            // all loads first: shared-memory loads cannot be scheduled across the stores below
+            __nv_bfloat162 rbv[8], kbv[8];
 #pragma unroll
             for (int tt = 0; tt < 8; ++tt) {
-                const int t = 16 * w4 + 8 * half + tt;
-                const uint32_t off = sw128_off(t, csw);
+                const uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
+                rbv[tt] = *reinterpret_cast<const __nv_bfloat162 *>(pt);
+                kbv[tt] = *reinterpret_cast<const __nv_bfloat162 *>(pt + kTile);
+            }
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) {
+                uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
                 const float2 xp = (tt == 0) ? make_float2(0.f, 0.f) : x[tt - 1];
-                const float2 er = make_float2(ex2f(xp.x - base.x), ex2f(xp.y - base.y));
-                const float2 ek = make_float2(ex2f(base.x - x[tt].x), ex2f(base.y - x[tt].y));
-                const float2 r2 = ld_bf2(sR + off), k2 = ld_bf2(sK + off);
-                bon[tt] = r2.x * u2.x * k2.x + r2.y * u2.y * k2.y;
-                const float2 rt = make_float2(r2.x * er.x, r2.y * er.y);
-                const float2 kt = make_float2(k2.x * ek.x, k2.y * ek.y);
-                st_bf2(sR + off, rt.x, rt.y);                       // r~  (A operand of the intra-chunk product)
-                st_bf2(sW + off, rt.x * fR.x, rt.y * fR.y);         // r^  (A operand against the incoming state)
-                st_bf2(sK + off, kt.x, kt.y);                       // k~  distance 0
-                st_bf2(sKH + off, kt.x * fK.x, kt.y * fK.y);        // k^  (state increment)
-                if (w4 <= 2) st_bf2(sKD + off, kt.x * fD[0].x, kt.y * fD[0].y);                 // rows [0,48)
-                if (w4 <= 1) st_bf2(sKD + 48 * 128 + off, kt.x * fD[1].x, kt.y * fD[1].y);      // rows [48,80)
-                if (w4 == 0) st_bf2(sKD + 80 * 128 + off, kt.x * fD[2].x, kt.y * fD[2].y);      // rows [80,96)
+                const float2 ea = add2(xp, nbase);                                   // c_{t-1} - c_ref
+                const float2 eb = make_float2(-nbase.x - x[tt].x, -nbase.y - x[tt].y);  // c_ref - c_t
+                const __nv_bfloat162 er = to_bf2(make_float2(ex2f(ea.x), ex2f(ea.y)));
+                const __nv_bfloat162 ek = to_bf2(make_float2(ex2f(eb.x), ex2f(eb.y)));
+                const __nv_bfloat162 rb = rbv[tt], kb = kbv[tt];
+                const float2 r2 = __bfloat1622float2(rb), k2 = __bfloat1622float2(kb);
+                const float2 rk = mul2(r2, k2);
+                bon[tt] = fmaf(rk.x, u2.x, rk.y * u2.y);
+                const __nv_bfloat162 rt = __hmul2(rb, er), kt = __hmul2(kb, ek);
+                if (WKV6_EXP & 1) { bon[tt] += __low2float(__hmul2(rt, fR)) + __low2float(__hmul2(kt, fK)) + __low2float(__hmul2(kt, fD[0])) + __low2float(__hmul2(kt, fD[1])) + __low2float(__hmul2(kt, fD[2])); continue; }
+                *reinterpret_cast<__nv_bfloat162 *>(pt) = rt;                                   // r~
+                *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rt, fR);          // r^ (over w)
+                *reinterpret_cast<__nv_bfloat162 *>(pt + kTile) = kt;                           // k~ distance 0
+                *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(kt, fK);                // k^
+                if (w4 <= 2) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo) = __hmul2(kt, fD[0]);              // rows [0,48)
+                if (w4 <= 1) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 48 * 128) = __hmul2(kt, fD[1]);   // rows [48,80)
+                if (w4 == 0) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 80 * 128) = __hmul2(kt, fD[2]);   // rows [80,96)
             }
             // sum the bonus partials over the 32 channel pairs: 8 values across 32 lanes in 9 shuffles
+            {
+                const bool up = (lane & 16) != 0;
 #pragma unroll
-            for (int hf = 4, bit = 16; hf >= 1; hf >>= 1, bit >>= 1) {
-                const bool up = (lane & bit) != 0;
-#pragma unroll
-                for (int i2 = 0; i2 < hf; ++i2) {
-                    const float send = up ? bon[i2] : bon[i2 + hf];
-                    const float keep = up ? bon[i2 + hf] : bon[i2];
-                    bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                for (int i2 = 0; i2 < 4; ++i2) {
+                    const float send = up ? bon[i2] : bon[i2 + 4];
+                    const float keep = up ? bon[i2 + 4] : bon[i2];
+                    bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
                 }
+            }
+            {
+                const bool up = (lane & 8) != 0;
+#pragma unroll
+                for (int i2 = 0; i2 < 2; ++i2) {
+                    const float send = up ? bon[i2] : bon[i2 + 2];
+                    const float keep = up ? bon[i2 + 2] : bon[i2];
+                    bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                }
+            }
+            {
+                const bool up = (lane & 4) != 0;
+                const float send = up ? bon[0] : bon[1];
+                const float keep = up ? bon[1] : bon[0];
+                bon[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
             }
             bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 2);
             bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 1);
@@ -326,12 +406,14 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             umma_commit(bar_mma1);
         }
         WKV6_TSTAMP(c, 4);
-        if (!mbar_wait(bar_mma1, c & 1)) err = 2;
+        if (!cta_wait(bar_mma1, c & 1, warp)) err = 2;
         tc_fence_after_sync();
         WKV6_TSTAMP(c, 5);
 
         // ---- epilogue of the intra-chunk matrix: pick, mask, round, store as the A operand of A v.
         // This warp covers column blocks J = 2*half and 2*half + 1 of row block I = w4.
+        const float bonus_a = sBonus[ta], bonus_b = sBonus[ta + 8];
+        const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
         {
             const int I = w4;
 #pragma unroll
@@ -353,17 +435,16 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                         for (int e = 0; e < 8; ++e) {
                             const int row = r0 + ((e & 2) ? 8 : 0);
                             const int col = 8 * (e >> 2) + 2 * q + (e & 1);
-                            f[e] = (col < row) ? f[e] : (col == row ? sBonus[16 * I + row] : 0.f);
+                            f[e] = (col < row) ? f[e] : (col == row ? ((e & 2) ? bonus_b : bonus_a) : 0.f);
                         }
                     }
                     o0 = pack_bf2(f[0], f[1]); o2 = pack_bf2(f[2], f[3]);
                     o1 = pack_bf2(f[4], f[5]); o3 = pack_bf2(f[6], f[7]);
                 }
-                const int s0 = 16 * J + 2 * q;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta, s0)) = o0;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta, s0 + 8)) = o1;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta + 8, s0)) = o2;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta + 8, s0 + 8)) = o3;
+                *reinterpret_cast<uint32_t *>(sAM + foA[2 * jj]) = o0;      // columns 16J + 2q
+                *reinterpret_cast<uint32_t *>(sAM + foA[2 * jj + 1]) = o1;  // columns 16J + 8 + 2q
+                *reinterpret_cast<uint32_t *>(sAM + foB[2 * jj]) = o2;
+                *reinterpret_cast<uint32_t *>(sAM + foB[2 * jj + 1]) = o3;
             }
         }
         // ---- state update in registers and its bf16 operand copy for the next chunk
@@ -371,16 +452,14 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             uint32_t v16[16];
             tmem_ld_16x256b_x4(tmS + wl + cb, v16);
             tmem_wait_ld();
-            const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 S[4 * nn + 0] = fmaf(S[4 * nn + 0], d0, __uint_as_float(v16[4 * nn + 0]));
                 S[4 * nn + 1] = fmaf(S[4 * nn + 1], d0, __uint_as_float(v16[4 * nn + 1]));
                 S[4 * nn + 2] = fmaf(S[4 * nn + 2], d1, __uint_as_float(v16[4 * nn + 2]));
                 S[4 * nn + 3] = fmaf(S[4 * nn + 3], d1, __uint_as_float(v16[4 * nn + 3]));
-                const int j = 8 * (n0 + nn) + 2 * q;
-                *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta, j)) = pack_bf2(S[4 * nn], S[4 * nn + 1]);
-                *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta + 8, j)) = pack_bf2(S[4 * nn + 2], S[4 * nn + 3]);
+                *reinterpret_cast<uint32_t *>(sSB + foA[nn]) = pack_bf2(S[4 * nn], S[4 * nn + 1]);
+                *reinterpret_cast<uint32_t *>(sSB + foB[nn]) = pack_bf2(S[4 * nn + 2], S[4 * nn + 3]);
             }
         }
         fence_proxy_async_smem();
@@ -402,7 +481,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             umma_commit(bar_mma2);
         }
         WKV6_TSTAMP(c, 7);
-        if (!mbar_wait(bar_mma2, c & 1)) err = 3;
+        if (!cta_wait(bar_mma2, c & 1, warp)) err = 3;
         tc_fence_after_sync();
         WKV6_TSTAMP(c, 8);
 
@@ -413,10 +492,9 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             tmem_wait_ld();
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
-                const int j = 8 * (n0 + nn) + 2 * q;
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta, j)) =
+                *reinterpret_cast<uint32_t *>(sAM + foA[nn]) =
                     pack_bf2(__uint_as_float(v16[4 * nn]), __uint_as_float(v16[4 * nn + 1]));
-                *reinterpret_cast<uint32_t *>(sAM + sw128_off(ta + 8, j)) =
+                *reinterpret_cast<uint32_t *>(sAM + foB[nn]) =
                     pack_bf2(__uint_as_float(v16[4 * nn + 2]), __uint_as_float(v16[4 * nn + 3]));
             }
         }
