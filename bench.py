@@ -38,8 +38,8 @@ FALLBACK_HBM_GBS = 6650.0
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--variant", default="auto", choices=["auto", "seq", "chunk"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
@@ -146,7 +146,7 @@ class ClockSampler:
     def start(self):
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                       "--format=csv,noheader,nounits", "-lms", "20"],
+                                       "--format=csv,noheader,nounits", "-lms", "200"],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
