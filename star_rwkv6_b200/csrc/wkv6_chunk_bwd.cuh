@@ -47,10 +47,12 @@ struct ChunkBwdSmem {
     static constexpr int oAB = oAM + kTile;         // bf16 copy of Abar [i][j]
     static constexpr int oHead = oAB + kTile;       // float [4][64] log2-decay sum of the first 8 tokens of a block
     static constexpr int oTot = oHead + 1024;       // float [4][64] log2-decay sum of the block
-    static constexpr int oRef = oTot + 1024;        // float [4][64] integer reference point of the block (chunk-relative, log2)
-    static constexpr int oOff = oRef + 1024;        // float [4][64] reference point relative to the block start
-    static constexpr int oFK = oOff + 1024;         // float [4][64] 2^{c_63 - ref(J)}
-    static constexpr int oDtot = oFK + 1024;        // float [64]    2^{c_63}
+    static constexpr int oOff = oTot + 1024;        // float [4][64] integer reference point of the block, relative to the block start
+    static constexpr int oFRb = oOff + 1024;        // bf16  [4][64] 2^{ref(I)}            (reference relative to the chunk start)
+    static constexpr int oFKb = oFRb + 512;         // bf16  [4][64] 2^{c_63 - ref(J)}
+    static constexpr int oMKb = oFKb + 512;         // bf16  [6][64] 2^{ref(J+d) - ref(J)}: d=1: J=0..2, d=2: J=0..1, d=3: J=0
+    static constexpr int oU = oMKb + 768;           // float [64]    u of this head
+    static constexpr int oDtot = oU + 256;          // float [64]    2^{c_63}
     static constexpr int oBonus = oDtot + 256;      // float [2][64]
     static constexpr int oVG = oBonus + 512;        // float [64]
     static constexpr int oT1 = oVG + 256;           // float [64]    <S_in, Abar>_i
@@ -151,8 +153,11 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     uint8_t *sS = smem + SM::oS, *sKH = smem + SM::oKH, *sKD = smem + SM::oKD, *sRD = smem + SM::oRD;
     uint8_t *sP = smem + SM::oP, *sAM = smem + SM::oAM, *sAB = smem + SM::oAB;
     float *sHead = reinterpret_cast<float *>(smem + SM::oHead), *sTot = reinterpret_cast<float *>(smem + SM::oTot);
-    float *sRef = reinterpret_cast<float *>(smem + SM::oRef), *sOff = reinterpret_cast<float *>(smem + SM::oOff);
-    float *sFK = reinterpret_cast<float *>(smem + SM::oFK), *sDtot = reinterpret_cast<float *>(smem + SM::oDtot);
+    float *sOff = reinterpret_cast<float *>(smem + SM::oOff), *sDtot = reinterpret_cast<float *>(smem + SM::oDtot);
+    __nv_bfloat16 *sFRb = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oFRb);
+    __nv_bfloat16 *sFKb = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oFKb);
+    __nv_bfloat16 *sMKb = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oMKb);
+    float *sU = reinterpret_cast<float *>(smem + SM::oU);
     float *sBonus = reinterpret_cast<float *>(smem + SM::oBonus), *sVG = reinterpret_cast<float *>(smem + SM::oVG);
     float *sXtot = reinterpret_cast<float *>(smem + SM::oXtot), *sBtot = reinterpret_cast<float *>(smem + SM::oBtot);
     float *sT1 = reinterpret_cast<float *>(smem + SM::oT1);
@@ -189,15 +194,13 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     float gu_acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) gu_acc[e] = 0.f;
-    float2 u_c[4];  // u of this thread's channel pairs
-    uint32_t fo[8];  // byte offsets of this thread's fragment elements in a swizzled tile: [2*nn + (row ta+8 ? 1 : 0)]
+    if (tid < 64) sU[tid] = load_any(a.u, a.u_dtype, (size_t)h * 64 + tid);
+    // byte offsets of this thread's fragment elements in a swizzled tile: row ta, column pair 8(n0+nn)+2q; row ta+8 is
+    // 1024 bytes further (same swizzle phase)
+    uint32_t fo4[4];
 #pragma unroll
-    for (int nn = 0; nn < 4; ++nn) {
-        const int col = 8 * (n0 + nn) + 2 * q;
-        u_c[nn] = make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + col), load_any(a.u, a.u_dtype, (size_t)h * 64 + col + 1));
-        fo[2 * nn] = sw128_off(ta, col);
-        fo[2 * nn + 1] = sw128_off(ta + 8, col);
-    }
+    for (int nn = 0; nn < 4; ++nn) fo4[nn] = sw128_off(ta, 8 * (n0 + nn) + 2 * q);
+#define FO(nn, hrow) (fo4[nn] + 1024u * (hrow))
 
     fence_proxy_async_smem();
     tc_fence_before_sync();
@@ -251,7 +254,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         for (int nn = 0; nn < 4; ++nn) {
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
-                const uint32_t off = fo[2 * nn + hrow];
+                const uint32_t off = FO(nn, hrow);
                 rp[2 * nn + hrow] = *reinterpret_cast<const __nv_bfloat162 *>(sR + off);
                 kp[2 * nn + hrow] = *reinterpret_cast<const __nv_bfloat162 *>(sK + off);
                 const float2 e2 = mul2(ld_bf2(sW + off), make_float2(kLog2e, kLog2e));
@@ -286,19 +289,27 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
         WKV6_TSTAMP(it, 2);
 
-        // ---- per (block, channel) factors, one pair per thread
+        // ---- per (block, channel) factors, one pair per thread; the power-of-two ones are exact in bf16
         {
             const int J = tid >> 6, i = tid & 63;
-            float base = 0.f, mybase = 0.f, myref = 0.f;
+            float base = 0.f, mybase = 0.f, ref[4];
 #pragma unroll
             for (int J2 = 0; J2 < 4; ++J2) {
-                const float rf = rintf(base + sHead[J2 * 64 + i]);  // integer: block-pair factors become powers of two
-                if (J2 == J) { mybase = base; myref = rf; }
+                ref[J2] = rintf(base + sHead[J2 * 64 + i]);  // integer: block-pair factors become powers of two
+                if (J2 == J) mybase = base;
                 base += sTot[J2 * 64 + i];
             }
-            sRef[J * 64 + i] = myref;
+            float myref = ref[0];
+#pragma unroll
+            for (int J2 = 1; J2 < 4; ++J2) myref = (J2 == J) ? ref[J2] : myref;
             sOff[J * 64 + i] = myref - mybase;
-            sFK[J * 64 + i] = ex2f(base - myref);
+            sFRb[J * 64 + i] = __float2bfloat16_rn(pow2i(myref));
+            sFKb[J * 64 + i] = __float2bfloat16_rn(ex2f(base - myref));
+#pragma unroll
+            for (int J2 = 1; J2 < 4; ++J2) {  // copy of block J serving row block J2 = J + d
+                const int d = J2 - J;
+                if (d >= 1) sMKb[((d == 1 ? 0 : d == 2 ? 3 : 5) + J) * 64 + i] = __float2bfloat16_rn(pow2i(ref[J2] - myref));
+            }
             if (J == 0) sDtot[i] = ex2f(base);
         }
         __syncthreads();
@@ -312,25 +323,20 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
             for (int nn = 0; nn < 4; ++nn) {
                 const int col = 8 * (n0 + nn) + 2 * q;
                 const float2 of = *reinterpret_cast<const float2 *>(&sOff[w4 * 64 + col]);
-                const float2 rf = *reinterpret_cast<const float2 *>(&sRef[w4 * 64 + col]);
-                const __nv_bfloat162 fkb = to_bf2(*reinterpret_cast<const float2 *>(&sFK[w4 * 64 + col]));
-                const __nv_bfloat162 frb = to_bf2(make_float2(pow2i(rf.x), pow2i(rf.y)));
+                const float2 uc = *reinterpret_cast<const float2 *>(&sU[col]);
+                const __nv_bfloat162 fkb = *reinterpret_cast<const __nv_bfloat162 *>(&sFKb[w4 * 64 + col]);
+                const __nv_bfloat162 frb = *reinterpret_cast<const __nv_bfloat162 *>(&sFRb[w4 * 64 + col]);
                 __nv_bfloat162 mk[3], mr[3];  // power-of-two factors of the copies for block distances 1..3
 #pragma unroll
                 for (int d = 1; d <= 3; ++d) {
-                    mk[d - 1] = mr[d - 1] = to_bf2(make_float2(0.f, 0.f));
-                    if (w4 + d <= 3) {
-                        const float2 rt2 = *reinterpret_cast<const float2 *>(&sRef[(w4 + d) * 64 + col]);
-                        mk[d - 1] = to_bf2(make_float2(pow2i(rt2.x - rf.x), pow2i(rt2.y - rf.y)));
-                    }
-                    if (w4 - d >= 0) {
-                        const float2 rs2 = *reinterpret_cast<const float2 *>(&sRef[(w4 - d) * 64 + col]);
-                        mr[d - 1] = to_bf2(make_float2(pow2i(rf.x - rs2.x), pow2i(rf.y - rs2.y)));
-                    }
+                    const int row0 = (d == 1 ? 0 : d == 2 ? 3 : 5);
+                    mk[d - 1] = mr[d - 1] = frb;
+                    if (w4 + d <= 3) mk[d - 1] = *reinterpret_cast<const __nv_bfloat162 *>(&sMKb[(row0 + w4) * 64 + col]);
+                    if (w4 - d >= 0) mr[d - 1] = *reinterpret_cast<const __nv_bfloat162 *>(&sMKb[(row0 + w4 - d) * 64 + col]);
                 }
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
-                    const uint32_t off = fo[2 * nn + hrow];
+                    const uint32_t off = FO(nn, hrow);
                     const int e0 = 4 * nn + 2 * hrow;
                     const float2 ea = make_float2(cs[e0] - lw[e0] - of.x, cs[e0 + 1] - lw[e0 + 1] - of.y);
                     const float2 eb = make_float2(of.x - cs[e0], of.y - cs[e0 + 1]);
@@ -340,7 +346,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                     ekb[2 * nn + hrow] = ek;
                     const __nv_bfloat162 rb = rp[2 * nn + hrow], kb = kp[2 * nn + hrow];
                     const float2 rk = mul2(__bfloat1622float2(rb), __bfloat1622float2(kb));
-                    const float bon = fmaf(rk.x, u_c[nn].x, rk.y * u_c[nn].y);
+                    const float bon = fmaf(rk.x, uc.x, rk.y * uc.y);
                     if (hrow == 0) bon_a += bon; else bon_b += bon;
                     const __nv_bfloat162 rt = __hmul2(rb, er), kt = __hmul2(kb, ek);
                     *reinterpret_cast<__nv_bfloat162 *>(sR + off) = rt;
@@ -416,7 +422,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                     if (s0 + 1 == t) sVG[t] = x1;
                     x0 = (s0 < t) ? x0 : 0.f;
                     x1 = (s0 + 1 < t) ? x1 : 0.f;
-                    *reinterpret_cast<uint32_t *>(sP + fo[2 * nn + hrow]) = pack_bf2(x0, x1);
+                    *reinterpret_cast<uint32_t *>(sP + FO(nn, hrow)) = pack_bf2(x0, x1);
                 }
             }
             // A: this warp covers column blocks J = 2*half, 2*half+1 of row block I = w4; pick the copy per block pair
@@ -444,16 +450,16 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                     o0 = pack_bf2(g8[0], g8[1]); o2 = pack_bf2(g8[2], g8[3]);
                     o1 = pack_bf2(g8[4], g8[5]); o3 = pack_bf2(g8[6], g8[7]);
                 }
-                *reinterpret_cast<uint32_t *>(sAM + fo[4 * jj]) = o0;
-                *reinterpret_cast<uint32_t *>(sAM + fo[4 * jj + 2]) = o1;
-                *reinterpret_cast<uint32_t *>(sAM + fo[4 * jj + 1]) = o2;
-                *reinterpret_cast<uint32_t *>(sAM + fo[4 * jj + 3]) = o3;
+                *reinterpret_cast<uint32_t *>(sAM + FO(2 * jj, 0)) = o0;
+                *reinterpret_cast<uint32_t *>(sAM + FO(2 * jj + 1, 0)) = o1;
+                *reinterpret_cast<uint32_t *>(sAM + FO(2 * jj, 1)) = o2;
+                *reinterpret_cast<uint32_t *>(sAM + FO(2 * jj + 1, 1)) = o3;
             }
             // <S_in, Abar>_i with the reverse state at the chunk end (before its update), for gw
             float za = 0.f, zb = 0.f;
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
-                const float2 sa = ld_bf2(sS + fo[2 * nn]), sb = ld_bf2(sS + fo[2 * nn + 1]);
+                const float2 sa = ld_bf2(sS + FO(nn, 0)), sb = ld_bf2(sS + FO(nn, 1));
                 za = fmaf(AB[4 * nn], sa.x, fmaf(AB[4 * nn + 1], sa.y, za));
                 zb = fmaf(AB[4 * nn + 2], sb.x, fmaf(AB[4 * nn + 3], sb.y, zb));
             }
@@ -471,8 +477,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 AB[4 * nn + 1] = fmaf(AB[4 * nn + 1], d0, f[4 * nn + 1]);
                 AB[4 * nn + 2] = fmaf(AB[4 * nn + 2], d1, f[4 * nn + 2]);
                 AB[4 * nn + 3] = fmaf(AB[4 * nn + 3], d1, f[4 * nn + 3]);
-                *reinterpret_cast<uint32_t *>(sAB + fo[2 * nn]) = pack_bf2(AB[4 * nn], AB[4 * nn + 1]);
-                *reinterpret_cast<uint32_t *>(sAB + fo[2 * nn + 1]) = pack_bf2(AB[4 * nn + 2], AB[4 * nn + 3]);
+                *reinterpret_cast<uint32_t *>(sAB + FO(nn, 0)) = pack_bf2(AB[4 * nn], AB[4 * nn + 1]);
+                *reinterpret_cast<uint32_t *>(sAB + FO(nn, 1)) = pack_bf2(AB[4 * nn + 2], AB[4 * nn + 3]);
             }
         }
         fence_proxy_async_smem();
@@ -528,9 +534,9 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 tmem_ld_16x256b_x1(tmA + lo + cb + 8 * nn, h1);    // GK1
                 tmem_ld_16x256b_x1(tmGK2 + lo + cb + 8 * nn, h2);  // GK2
                 tmem_wait_ld();
-                const float2 rf = *reinterpret_cast<const float2 *>(&sRef[w4 * 64 + col]);
-                const float2 fr = make_float2(pow2i(rf.x), pow2i(rf.y));
-                const float2 fk = *reinterpret_cast<const float2 *>(&sFK[w4 * 64 + col]);
+                const float2 fr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&sFRb[w4 * 64 + col]));
+                const float2 fk = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&sFKb[w4 * 64 + col]));
+                const float2 uc = *reinterpret_cast<const float2 *>(&sU[col]);
                 float qv[4], bsum0 = 0.f, bsum1 = 0.f;
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
@@ -542,12 +548,12 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                     const float2 kt = __bfloat1622float2(__hmul2(kp[2 * nn + hrow], ekb[2 * nn + hrow]));
                     const float2 G1 = make_float2(g1[2 * hrow], g1[2 * hrow + 1]), G2 = make_float2(g2[2 * hrow], g2[2 * hrow + 1]);
                     const float2 H1 = make_float2(h1[2 * hrow], h1[2 * hrow + 1]), H2 = make_float2(h2[2 * hrow], h2[2 * hrow + 1]);
-                    const float2 uvg = make_float2(u_c[nn].x * vg, u_c[nn].y * vg);
+                    const float2 uvg = make_float2(uc.x * vg, uc.y * vg);
                     // gr = Er (GR1 + fR GR2) + u k vg ;  gk = Ek (GK1 + fK GK2) + u r vg
                     const float2 gr = fma2(er, fma2(fr, G2, G1), mul2(uvg, k2));
                     const float2 gk = fma2(ek, fma2(fk, H2, H1), mul2(uvg, r2));
-                    *reinterpret_cast<__nv_bfloat162 *>(sP + fo[2 * nn + hrow]) = to_bf2(gr);
-                    *reinterpret_cast<__nv_bfloat162 *>(sAM + fo[2 * nn + hrow]) = to_bf2(gk);
+                    *reinterpret_cast<__nv_bfloat162 *>(sP + FO(nn, hrow)) = to_bf2(gr);
+                    *reinterpret_cast<__nv_bfloat162 *>(sAM + FO(nn, hrow)) = to_bf2(gk);
                     // gw pieces: a = r~ GR1 + r^ GR2, z = k~ GK1, b = k^ GK2
                     const float2 av = fma2(rt, G1, mul2(mul2(rt, fr), G2));
                     const float2 zv = mul2(kt, H1);
@@ -580,8 +586,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
             tmem_ld_16x256b_x4(tmGV + lo + cb, gv16);
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
-                *reinterpret_cast<uint32_t *>(sKD + fo[2 * nn]) = pack_bf2(gv16[4 * nn], gv16[4 * nn + 1]);
-                *reinterpret_cast<uint32_t *>(sKD + fo[2 * nn + 1]) = pack_bf2(gv16[4 * nn + 2], gv16[4 * nn + 3]);
+                *reinterpret_cast<uint32_t *>(sKD + FO(nn, 0)) = pack_bf2(gv16[4 * nn], gv16[4 * nn + 1]);
+                *reinterpret_cast<uint32_t *>(sKD + FO(nn, 1)) = pack_bf2(gv16[4 * nn + 2], gv16[4 * nn + 3]);
             }
         }
         tc_fence_before_sync();
@@ -606,7 +612,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 float2 gw = mul2(mul2(lwf, make_float2(1.0f / kLog2e, 1.0f / kLog2e)),
                                  make_float2(base.x + loc[e0], base.y + loc[e0 + 1]));  // -exp(w) = log-decay
                 if (c == 0 && ta + 8 * hrow == 0) gw = make_float2(0.f, 0.f);  // zero initial state: no dependence on w_0
-                *reinterpret_cast<__nv_bfloat162 *>(sRD + fo[2 * nn + hrow]) = to_bf2(gw);
+                *reinterpret_cast<__nv_bfloat162 *>(sRD + FO(nn, hrow)) = to_bf2(gw);
             }
         }
         fence_proxy_async_smem();
