@@ -26,6 +26,7 @@
 //
 // Tensor-memory map (256 columns): lanes 0-15: [0,64) P -> GR1 | [64,128) A (distance 0) -> GK1 | [128,192) GR2 | [192,256) GK2
 //                                  lanes 16-31: [0,64) Abar increment | [64,128) gv | [128,224) A (distances 1..3)
+//                                               | [224,256) per-thread stash of the bf16 log-decays until gw is formed
 #pragma once
 
 #include "wkv6_chunk_fwd.cuh"
@@ -55,11 +56,11 @@ struct ChunkBwdSmem {
     static constexpr int oDtot = oU + 256;          // float [64]    2^{c_63}
     static constexpr int oBonus = oDtot + 256;      // float [2][64]
     static constexpr int oVG = oBonus + 512;        // float [64]
-    static constexpr int oT1 = oVG + 256;           // float [64]    <S_in, Abar>_i
+    static constexpr int oT1 = oVG + 256;           // float [2][64] <S_in, Abar>_i, one partial per column half
     static constexpr int oXtot = oTot;              // float [4][64] block sums for gw (sTot is dead by then)
     static constexpr int oBtot = oHead;             // float [4][64] block sums for gw (sHead is dead by then)
     static constexpr int oGU = oHead;               // float [4][64] final reduction of gu (after the last chunk)
-    static constexpr int oBar = oT1 + 256;          // full, mma1, mma2
+    static constexpr int oBar = oT1 + 512;          // full, mma1, mma2
     static constexpr int oSlot = oBar + 32;
     static constexpr int kBytes = oSlot + 16;
     static constexpr int kAlloc = kBytes;
@@ -211,6 +212,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     const uint32_t tmP = tbase, tmA = tbase + 64, tmGR2 = tbase + 128, tmGK2 = tbase + 192;
     const uint32_t tmAN = tbase + (16u << 16), tmGV = tbase + (16u << 16) + 64, tmAD = tbase + (16u << 16) + 128;
     const uint32_t cb = 8 * n0;  // first accumulator column of this thread's fragment
+    const uint32_t tmStash = tbase + (16u << 16) + lo + 224 + 16 * half;  // 16 columns x 16 lanes per warp: 8 registers per thread
 
     auto issue_loads = [&](int c) {
         mbar_expect_tx(bar_full, 6 * kTile);
@@ -247,7 +249,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
 
         // ---- per-step log2 decays and their running sums inside the block (fragment layout)
         __nv_bfloat162 rp[8], kp[8];  // raw r, k pairs: index 2*nn + (row ta+8 ? 1 : 0)
-        __nv_bfloat162 erb[8], ekb[8], lwb[8];  // e^{c_{t-1}-ref}, e^{ref-c_t}, log2-decay, rounded to bf16
+        __nv_bfloat162 erb[8], ekb[8];  // e^{c_{t-1}-ref}, e^{ref-c_t}, rounded to bf16
+        uint32_t lwst[8];               // log2-decays rounded to bf16, parked in tensor memory until gw is formed
         float cs[16], lw[16];
         const bool full_chunk = (c + 1) * kChunk <= a.T;
 #pragma unroll
@@ -264,9 +267,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 if (!full_chunk && c * kChunk + ta + 8 * hrow >= a.T) l2 = make_float2(0.f, 0.f);
                 lw[4 * nn + 2 * hrow] = l2.x;
                 lw[4 * nn + 2 * hrow + 1] = l2.y;
-                lwb[2 * nn + hrow] = to_bf2(l2);
+                { const __nv_bfloat162 lb = to_bf2(l2); lwst[2 * nn + hrow] = *reinterpret_cast<const uint32_t *>(&lb); }
             }
         }
+        tmem_st_16x256b_x2(tmStash, lwst);
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn)
 #pragma unroll
@@ -284,7 +288,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 *reinterpret_cast<float2 *>(&sTot[w4 * 64 + col]) = make_float2(cs[4 * nn + 2], cs[4 * nn + 3]);
             }
         }
-        if (tid < 64) sT1[tid] = 0.f;  // accumulated in epilogue 1
+        tmem_wait_st();
         if (tid == 0) bulk_wait_read<0>();  // the previous chunk's output tiles have left shared memory
         if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
         WKV6_TSTAMP(it, 2);
@@ -465,10 +469,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
             }
             za += __shfl_xor_sync(0xffffffffu, za, 1); za += __shfl_xor_sync(0xffffffffu, za, 2);
             zb += __shfl_xor_sync(0xffffffffu, zb, 1); zb += __shfl_xor_sync(0xffffffffu, zb, 2);
-            if (q == 0) {  // two contributions per slot (the two column halves): the sum is order-independent
-                atomicAdd(&sT1[ta], za);
-                atomicAdd(&sT1[ta + 8], zb);
-            }
+            if (q == 0) { sT1[half * 64 + ta] = za; sT1[half * 64 + ta + 8] = zb; }
             tmem_ld_16x256b_x4(tmAN + lo + cb, f);  // rows are key channels here
             const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
 #pragma unroll
@@ -594,10 +595,13 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         __syncthreads();
         WKV6_TSTAMP(it, 10);
         // G_t = e^{c_63} <S_in, Abar> + sum_all b + sum_{later blocks} q + (suffix_incl(q) - a)_t ;  gw = -exp(w) G
+        uint32_t lwst2[8];
+        tmem_ld_16x256b_x2(tmStash, lwst2);
+        tmem_wait_ld();
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn) {
             const int col = 8 * (n0 + nn) + 2 * q;
-            const float2 t1 = *reinterpret_cast<const float2 *>(&sT1[col]);
+            const float2 t1 = add2(*reinterpret_cast<const float2 *>(&sT1[col]), *reinterpret_cast<const float2 *>(&sT1[64 + col]));
             const float2 dt = *reinterpret_cast<const float2 *>(&sDtot[col]);
             float2 base = mul2(t1, dt);
 #pragma unroll
@@ -608,7 +612,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const int e0 = 4 * nn + 2 * hrow;
-                const float2 lwf = __bfloat1622float2(lwb[2 * nn + hrow]);
+                const float2 lwf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&lwst2[2 * nn + hrow]));
                 float2 gw = mul2(mul2(lwf, make_float2(1.0f / kLog2e, 1.0f / kLog2e)),
                                  make_float2(base.x + loc[e0], base.y + loc[e0 + 1]));  // -exp(w) = log-decay
                 if (c == 0 && ta + 8 * hrow == 0) gw = make_float2(0.f, 0.f);  // zero initial state: no dependence on w_0
