@@ -164,7 +164,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     float *sT1 = reinterpret_cast<float *>(smem + SM::oT1);
     float *sGU = reinterpret_cast<float *>(smem + SM::oGU);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SM::oBar);
-    uint64_t *bar_full = bars, *bar_mma1 = bars + 1, *bar_mma2 = bars + 2;
+    // bar_full: w, r, k tiles (needed first); bar_late: v, gy and the checkpointed state (needed by the first MMA group)
+    uint64_t *bar_full = bars, *bar_mma1 = bars + 1, *bar_mma2 = bars + 2, *bar_late = bars + 3;
     uint32_t *slot = reinterpret_cast<uint32_t *>(smem + SM::oSlot);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -176,6 +177,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
 
     if (tid == 0) {
         mbar_init(bar_full, 1);
+        mbar_init(bar_late, 1);
         mbar_init(bar_mma1, 4);  // four issuing threads
         mbar_init(bar_mma2, 3);  // three issuing threads
         fence_mbar_init();
@@ -215,13 +217,14 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     const uint32_t tmStash = tbase + (16u << 16) + lo + 224 + 16 * half;  // 16 columns x 16 lanes per warp: 8 registers per thread
 
     auto issue_loads = [&](int c) {
-        mbar_expect_tx(bar_full, 6 * kTile);
+        mbar_expect_tx(bar_full, 3 * kTile);
+        tma_load_3d(sW, &tm_w, bar_full, h * 64, c * kChunk, b);
         tma_load_3d(sR, &tm_r, bar_full, h * 64, c * kChunk, b);
         tma_load_3d(sK, &tm_k, bar_full, h * 64, c * kChunk, b);
-        tma_load_3d(sV, &tm_v, bar_full, h * 64, c * kChunk, b);
-        tma_load_3d(sW, &tm_w, bar_full, h * 64, c * kChunk, b);
-        tma_load_3d(sG, &tm_gy, bar_full, h * 64, c * kChunk, b);
-        bulk_load(sS, a.ckpt + ((size_t)blockIdx.x * nchunks + c) * 4096, kTile, bar_full);
+        mbar_expect_tx(bar_late, 3 * kTile);
+        tma_load_3d(sV, &tm_v, bar_late, h * 64, c * kChunk, b);
+        tma_load_3d(sG, &tm_gy, bar_late, h * 64, c * kChunk, b);
+        bulk_load(sS, a.ckpt + ((size_t)blockIdx.x * nchunks + c) * 4096, kTile, bar_late);
     };
     if (tid == 0) issue_loads(nchunks - 1);
 
@@ -372,7 +375,11 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        __syncthreads();
+        {
+            bool ok = true;
+            if (warp == 0) ok = mbar_wait(bar_late, it & 1);  // v, gy, S_in have landed (long ago, normally)
+            if (!__syncthreads_and(ok && err == 0)) { err = err ? err : 4; break; }
+        }
         WKV6_TSTAMP(it, 4);
 
         // ---- MMA group 1, four issuing threads (independent accumulators)
@@ -636,7 +643,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         if (err != 0) {
             if (load_pending)
                 for (uint32_t k2 = 0; k2 < (1u << 16); ++k2)
-                    if (mbar_try_wait(bar_full, 0) || mbar_try_wait(bar_full, 1)) break;
+                    if ((mbar_try_wait(bar_full, 0) || mbar_try_wait(bar_full, 1)) &&
+                        (mbar_try_wait(bar_late, 0) || mbar_try_wait(bar_late, 1))) break;
             atomicExch(&g_chunk_status, 100 + err);
         }
         bulk_wait<0>();
