@@ -137,6 +137,30 @@ WKV6_API int wkv6_backward_static_scratch(const wkv6_problem *p, const void *r, 
 WKV6_API size_t wkv6_static_scratch_bytes(void);
 
 /*
+ * Sequence splitting along T (no counterpart in the reference, whose kernels cap T at a compile-time constant and
+ * never split a sequence; BASELINE's long-sequence configuration asks for it).  A sequence cut into G segments is
+ * handled as a batch of B*G shorter sequences (a dense [B, G*Tseg, C] tensor is a [B*G, Tseg, C] tensor) whose
+ * segment g starts from the state the segments before it produce:
+ *   1. wkv6_segment_summary: per segment, the state it builds from zero (state_out [B*G,H,N,N] fp32) and the log2
+ *      of its total decay per key channel (dec_log2_out [B*G,H,N]).  reverse = 0: x1 = k, x2 = v (forward state).
+ *      reverse = 1: x1 = r, x2 = gy (the reverse state of the backward).
+ *   2. wkv6_state_scan: exclusive scan over g of the maps S -> 2^dec S + state (ascending g, seeded with s0
+ *      [B,H,N,N] or zero; descending g when reverse).  state_in_out[b*G+g] = state entering segment g;
+ *      last_out (optional, [B,H,N,N]) = state after the last segment.  Across GPUs the summaries of all ranks are
+ *      gathered (they are small: H*(N*N+N)*4 bytes per segment) and every rank runs the same scan.
+ *   3. wkv6_forward on the [B*G, Tseg, C] problem with s_in = the scanned states (and a ckpt buffer), and
+ *      wkv6_backward_seeded with ab_in = the scanned reverse states [B*G,H,N,N] fp32 and that ckpt buffer.
+ * Chunked variant only (N == 64, bf16 r,k,v,w,y).
+ */
+WKV6_API int wkv6_segment_summary(const wkv6_problem *p, const void *x1, const void *x2, const void *w, int reverse,
+                                  float *state_out, float *dec_log2_out, void *stream);
+WKV6_API int wkv6_state_scan(int32_t B, int32_t H, int32_t N, int32_t G, const float *dec_log2, const float *state_sum,
+                             const float *s0, float *state_in_out, float *last_out, int reverse, void *stream);
+WKV6_API int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
+                                  const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu,
+                                  const void *ckpt, const float *ab_in, void *stream);
+
+/*
  * XLA legacy custom-call surface.  The library also exports the C++ symbols gpu_ops::rwkv_forward_fn,
  * gpu_ops::rwkv_backward_fn and gpu_ops::rwkv_forward_with_state_fn with the signature
  *     void f(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len)

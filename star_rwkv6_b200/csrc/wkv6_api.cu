@@ -152,4 +152,39 @@ int wkv6_backward(const wkv6_problem *p, const void *r, const void *k, const voi
     return seq_backward(p, d, r, k, v, w, u, gy, gr, gk, gv, gw, gu, workspace, workspace_bytes, st);
 }
 
+int wkv6_segment_summary(const wkv6_problem *p, const void *x1, const void *x2, const void *w, int reverse,
+                         float *state_out, float *dec_log2_out, void *stream) {
+    Dims d;
+    int rc = validate(p, &d);
+    if (rc) return rc;
+    if (!chunk_supported(p)) return fail(WKV6_ERR_UNSUPPORTED, "segment summaries need the chunked variant (N == 64, bf16)");
+    if (p->B == 0 || p->H == 0) return WKV6_OK;
+    WKV6_CHECK_PTR(x1); WKV6_CHECK_PTR(x2); WKV6_CHECK_PTR(w); WKV6_CHECK_PTR(state_out); WKV6_CHECK_PTR(dec_log2_out);
+    return chunk_segment_summary(p, d, x1, x2, w, reverse != 0, state_out, dec_log2_out, static_cast<cudaStream_t>(stream));
+}
+
+int wkv6_state_scan(int32_t B, int32_t H, int32_t N, int32_t G, const float *dec_log2, const float *state_sum,
+                    const float *s0, float *state_in_out, float *last_out, int reverse, void *stream) {
+    if (N != 64) return fail(WKV6_ERR_UNSUPPORTED, "state scan is built for N == 64");
+    if (B < 0 || H < 0 || G < 1) return fail(WKV6_ERR_INVALID, "bad B/H/G (%d,%d,%d)", B, H, G);
+    if (dec_log2 == nullptr || state_sum == nullptr || state_in_out == nullptr) return fail(WKV6_ERR_INVALID, "NULL argument");
+    return chunk_state_scan(B, H, G, dec_log2, state_sum, s0, state_in_out, last_out, reverse != 0, static_cast<cudaStream_t>(stream));
+}
+
+int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w, const void *u,
+                         const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu, const void *ckpt,
+                         const float *ab_in, void *stream) {
+    Dims d;
+    int rc = validate(p, &d);
+    if (rc) return rc;
+    if (!chunk_supported(p)) return fail(WKV6_ERR_UNSUPPORTED, "the seeded backward needs the chunked variant (N == 64, bf16)");
+    if (ckpt == nullptr) return fail(WKV6_ERR_INVALID, "the seeded backward needs the checkpoints of the matching forward");
+    if (p->B == 0 || p->H == 0 || p->T == 0) return WKV6_OK;
+    WKV6_CHECK_PTR(r); WKV6_CHECK_PTR(k); WKV6_CHECK_PTR(v); WKV6_CHECK_PTR(w); WKV6_CHECK_PTR(gy);
+    WKV6_CHECK_PTR(gr); WKV6_CHECK_PTR(gk); WKV6_CHECK_PTR(gv); WKV6_CHECK_PTR(gw);
+    if (u == nullptr || gu == nullptr) return fail(WKV6_ERR_INVALID, "u or gu is NULL");
+    return chunk_backward_seeded(p, d, r, k, v, w, u, gy, gr, gk, gv, gw, gu, ckpt, ab_in, nullptr, 0,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

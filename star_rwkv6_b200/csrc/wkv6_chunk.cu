@@ -56,7 +56,8 @@ int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const voi
     if ((rc = make_map(&my, y ? y : r, p, d, "y"))) return rc;  // y == NULL: states only, the map is never used
     ChunkFwdArgs a{};
     a.u = u; a.u_dtype = p->u_dtype; a.s_in = s_in; a.s_map = s_map; a.s_kinds = s_kinds; a.s_dtype = p->s_dtype;
-    a.s_out = s_out; a.write_y = (y != nullptr); a.ckpt = static_cast<__nv_bfloat16 *>(ckpt); a.B = p->B; a.T = p->T; a.H = p->H;
+    a.s_out = s_out; a.write_y = (y != nullptr); a.ckpt = static_cast<__nv_bfloat16 *>(ckpt);
+    a.reverse_state = false; a.dec_out = nullptr; a.B = p->B; a.T = p->T; a.H = p->H;
     cudaError_t e = cudaFuncSetAttribute(chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ChunkFwdSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_fwd_kernel)");
@@ -74,6 +75,12 @@ size_t chunk_backward_workspace(const wkv6_problem *p, const Dims &, int have_ck
 int chunk_backward(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v, const void *w,
                    const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu, const void *ckpt,
                    void *ws, size_t ws_bytes, cudaStream_t st) {
+    return chunk_backward_seeded(p, d, r, k, v, w, u, gy, gr, gk, gv, gw, gu, ckpt, nullptr, ws, ws_bytes, st);
+}
+
+int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v,
+                          const void *w, const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw,
+                          void *gu, const void *ckpt, const float *ab_in, void *ws, size_t ws_bytes, cudaStream_t st) {
     int rc;
     if (ckpt == nullptr) {
         const size_t need = chunk_ckpt_bytes(p);
@@ -95,12 +102,64 @@ int chunk_backward(const wkv6_problem *p, const Dims &d, const void *r, const vo
     ChunkBwdArgs a{};
     a.u = u; a.u_dtype = p->u_dtype; a.gu = gu; a.gu_dtype = p->gu_dtype;
     a.ckpt = static_cast<const __nv_bfloat16 *>(ckpt); a.B = p->B; a.T = p->T; a.H = p->H;
+    a.ab_in = ab_in; a.zero_init = (ab_in == nullptr);  // a seeded call is one segment of a longer sequence
     cudaError_t e = cudaFuncSetAttribute(chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ChunkBwdSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_kernel)");
     chunk_bwd_kernel<<<p->B * p->H, 256, ChunkBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
     e = cudaGetLastError();
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_bwd_kernel launch");
+}
+
+// Summary of every sequence as an affine map of the state: log2 of the total decay per key channel and the state
+// the sequence builds from zero.  Forward direction: x1 = k, x2 = v.  Reverse direction (the backward's state):
+// x1 = r, x2 = gy.  It is the forward kernel with its y output suppressed.
+int chunk_segment_summary(const wkv6_problem *p, const Dims &d, const void *x1, const void *x2, const void *w,
+                          bool reverse, float *b_out, float *dec_log2_out, cudaStream_t st) {
+    CUtensorMap m1, m2, mw;
+    int rc;
+    if ((rc = make_map(&m1, x1, p, d, "x1"))) return rc;
+    if ((rc = make_map(&m2, x2, p, d, "x2"))) return rc;
+    if ((rc = make_map(&mw, w, p, d, "w"))) return rc;
+    ChunkFwdArgs a{};
+    a.u = nullptr; a.u_dtype = WKV6_F32; a.s_dtype = WKV6_F32; a.s_out = b_out; a.B = p->B; a.T = p->T; a.H = p->H;
+    a.write_y = false; a.reverse_state = reverse; a.dec_out = dec_log2_out;
+    cudaError_t e = cudaFuncSetAttribute(chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ChunkFwdSmem::kAlloc);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_fwd_kernel)");
+    chunk_fwd_kernel<<<p->B * p->H, 256, ChunkFwdSmem::kAlloc, st>>>(m1, m1, m2, mw, m1, a);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_fwd_kernel (summary) launch");
+}
+
+// Exclusive scan of affine state maps over the G segments of each sequence:
+//   forward : S_in[g] = state entering segment g      = 2^{dec[g-1]} S_in[g-1] + b[g-1],  S_in[0] = s0 (or 0)
+//   reverse : A_in[g] = reverse state entering at the end of segment g = 2^{dec[g+1]} A_in[g+1] + b[g+1],  A_in[G-1] = 0
+// Segment g of sequence (b, h) sits at batch index b*G + g of the [B*G, H, ...] summary arrays.
+__global__ void state_scan_kernel(int B, int H, int G, const float *__restrict__ dec, const float *__restrict__ bsum,
+                                  const float *__restrict__ s0, float *__restrict__ out, float *__restrict__ last,
+                                  bool reverse) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // over B*H*64*64
+    if (idx >= (size_t)B * H * 4096) return;
+    const int ij = (int)(idx & 4095), i = ij >> 6;
+    const int h = (int)((idx >> 12) % H), b = (int)(idx / ((size_t)H * 4096));
+    float s = (!reverse && s0 != nullptr) ? s0[idx] : 0.f;
+    for (int gg = 0; gg < G; ++gg) {
+        const int g = reverse ? G - 1 - gg : gg;
+        const size_t seq = ((size_t)(b * G + g) * H + h);
+        out[seq * 4096 + ij] = s;
+        s = fmaf(exp2f(dec[seq * 64 + i]), s, bsum[seq * 4096 + ij]);
+    }
+    if (last != nullptr) last[idx] = s;
+}
+
+int chunk_state_scan(int B, int H, int G, const float *dec, const float *bsum, const float *s0, float *out, float *last,
+                     bool reverse, cudaStream_t st) {
+    const size_t n = (size_t)B * H * 4096;
+    if (n == 0 || G <= 0) return WKV6_OK;
+    state_scan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(B, H, G, dec, bsum, s0, out, last, reverse);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "state_scan_kernel launch");
 }
 
 int chunk_status() {

@@ -70,6 +70,8 @@ struct ChunkBwdArgs {
     const void *u; int u_dtype;
     void *gu; int gu_dtype;
     const __nv_bfloat16 *ckpt;
+    const float *ab_in;  // optional [B*H][64][64]: reverse state entering at the end of the sequence (zero if NULL)
+    bool zero_init;      // the forward started from a zero state: gw at t = 0 is exactly zero
     int B, T, H;
 };
 
@@ -192,8 +194,16 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     // zero: the reverse state (registers + operand copy)
     float AB[16];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) AB[e] = 0.f;
-    for (int o = tid * 16; o < kTile; o += 256 * 16) *reinterpret_cast<uint4 *>(sAB + o) = make_uint4(0, 0, 0, 0);
+    for (int nn = 0; nn < 4; ++nn) {
+        const int j0 = 8 * (n0 + nn) + 2 * q;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = ta + (e >= 2 ? 8 : 0);
+            AB[4 * nn + e] = a.ab_in ? a.ab_in[(size_t)blockIdx.x * 4096 + (size_t)i * 64 + j0 + (e & 1)] : 0.f;
+        }
+        *reinterpret_cast<uint32_t *>(sAB + sw128_off(ta, j0)) = pack_bf2(AB[4 * nn], AB[4 * nn + 1]);
+        *reinterpret_cast<uint32_t *>(sAB + sw128_off(ta + 8, j0)) = pack_bf2(AB[4 * nn + 2], AB[4 * nn + 3]);
+    }
     float gu_acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) gu_acc[e] = 0.f;
@@ -622,7 +632,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 const float2 lwf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&lwst2[2 * nn + hrow]));
                 float2 gw = mul2(mul2(lwf, make_float2(1.0f / kLog2e, 1.0f / kLog2e)),
                                  make_float2(base.x + loc[e0], base.y + loc[e0 + 1]));  // -exp(w) = log-decay
-                if (c == 0 && ta + 8 * hrow == 0) gw = make_float2(0.f, 0.f);  // zero initial state: no dependence on w_0
+                if (a.zero_init && c == 0 && ta + 8 * hrow == 0) gw = make_float2(0.f, 0.f);  // no dependence on w_0
                 *reinterpret_cast<__nv_bfloat162 *>(sRD + FO(nn, hrow)) = to_bf2(gw);
             }
         }

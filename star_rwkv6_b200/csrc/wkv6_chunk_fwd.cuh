@@ -72,6 +72,11 @@ struct ChunkFwdArgs {
     __nv_bfloat16 *ckpt;  // optional [B*H][T/64][64*64] bf16 chunk-start states in operand (swizzled) layout
     int B, T, H;
     bool write_y;         // false: only states / checkpoints are produced
+    // Segment summaries (see wkv6_segment_summary): walk the chunks from last to first and accumulate
+    // sum_t (x1_t e^{c_{t-1}}) (x) x2_t instead of sum_t (x1_t e^{c_end - c_t}) (x) x2_t, i.e. the reverse state of the
+    // backward when x1 = r and x2 = gy are passed in the k and v slots.
+    bool reverse_state;
+    float *dec_out;       // optional [B*H][64]: log2 of the total decay of the sequence per key channel
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -195,8 +200,9 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta + 8, j)) = pack_bf2(S[4 * nn + 2], S[4 * nn + 3]);
         }
     }
-    const float2 u2 = make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane),
-                                  load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane + 1));
+    const float2 u2 = a.u == nullptr ? make_float2(0.f, 0.f)
+                                     : make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane),
+                                                   load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane + 1));
 
     fence_proxy_async_smem();
     tc_fence_before_sync();
@@ -214,8 +220,9 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         foB[nn] = sw128_off(ta + 8, 8 * (n0 + nn) + 2 * q);
     }
 
-    auto issue_loads = [&](int c) {
-        const int st = c & 1;
+    auto issue_loads = [&](int ic2) {
+        const int c = a.reverse_state ? nchunks - 1 - ic2 : ic2;
+        const int st = ic2 & 1;
         uint8_t *base = smem + st * SM::kStage;
         mbar_expect_tx(&bar_full[st], 4 * kTile);
         tma_load_3d(base, &tm_r, &bar_full[st], h * 64, c * kChunk, b);
@@ -245,14 +252,16 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
 
     int err = 0;
     int loads_pending = (nchunks > 1) ? 2 : 1;  // meaningful on thread 0 only
-    for (int c = 0; c < nchunks; ++c) {
-        const int st = c & 1;
+    float2 dsum = make_float2(0.f, 0.f);  // warp 0: log2 of the decay accumulated over all chunks, channels 2*lane, +1
+    for (int ic = 0; ic < nchunks; ++ic) {
+        const int c = a.reverse_state ? nchunks - 1 - ic : ic;  // chunk processed in this iteration
+        const int st = ic & 1;
         uint8_t *sR = smem + st * SM::kStage;  // this stage: r, k, v, w tiles at +0, +kTile, +2 kTile, +3 kTile
         const uint64_t so = (uint64_t)(st * (SM::kStage >> 4));
-        WKV6_TSTAMP(c, 0);
-        if (!cta_wait(&bar_full[st], (c >> 1) & 1, warp)) err = 1;
+        WKV6_TSTAMP(ic, 0);
+        if (!cta_wait(&bar_full[st], (ic >> 1) & 1, warp)) err = 1;
         if (tid == 0) --loads_pending;
-        WKV6_TSTAMP(c, 1);
+        WKV6_TSTAMP(ic, 1);
 
         // ---- pass 1: per-step log2 decays of this thread's 8 tokens x 2 channels, running sums from the first of them.
         // Row t = 16*w4 + 8*half + tt has swizzle phase tt, so one per-thread base pointer plus a per-tt XOR term
@@ -280,7 +289,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         // the previous chunk's y tile and checkpoint copies must have left shared memory before it is rewritten
         if (tid == 0) bulk_wait_read<0>();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
-        WKV6_TSTAMP(c, 2);
+        WKV6_TSTAMP(ic, 2);
 
         // ---- pass 2: scaled operands.  The block reference is the boundary between the two token halves, so the
         // running sums of the second half are already relative to it and those of the first half need only -head.
@@ -320,6 +329,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             if (warp == 0) {
                 const float2 all = make_float2(head.x + tail.x + post.x, head.y + tail.y + post.y);
                 *reinterpret_cast<float2 *>(&sDtot[2 * lane]) = make_float2(ex2f(all.x), ex2f(all.y));
+                dsum = add2(dsum, all);
             }
             float bon[8];
             const int kdo = (int)(sKD - sR), kho = (int)(sKH - sR);  // uniform offsets of the copy tiles from this stage
@@ -393,7 +403,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
-        WKV6_TSTAMP(c, 3);
+        WKV6_TSTAMP(ic, 3);
 
         if (tid == 0) {
             tc_fence_after_sync();
@@ -407,17 +417,17 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         } else if (tid == 32) {
             tc_fence_after_sync();
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // state increment = k^^T v
-                umma_ss(tmS, dKH + 128 * kk, dV + so + 128 * kk, idMM, kk > 0);
+            for (int kk = 0; kk < 4; ++kk)  // state increment = k^^T v   (reverse-state mode: r^^T x2, r^ sits in the w tile)
+                umma_ss(tmS, (a.reverse_state ? dW + so : dKH) + 128 * kk, dV + so + 128 * kk, idMM, kk > 0);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // y = r^ S_in
                 umma_ss(tmY, dW + so + 2 * kk, dSB + 128 * kk, idKM, kk > 0);
             umma_commit(bar_mma1);
         }
-        WKV6_TSTAMP(c, 4);
-        if (!cta_wait(bar_mma1, c & 1, warp)) err = 2;
+        WKV6_TSTAMP(ic, 4);
+        if (!cta_wait(bar_mma1, ic & 1, warp)) err = 2;
         tc_fence_after_sync();
-        WKV6_TSTAMP(c, 5);
+        WKV6_TSTAMP(ic, 5);
 
         // ---- epilogue of the intra-chunk matrix: pick, mask, round, store as the A operand of A v.
         // This warp covers column blocks J = 2*half and 2*half + 1 of row block I = w4.
@@ -474,13 +484,13 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         fence_proxy_async_smem();
         tc_fence_before_sync();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 11; break; }
-        WKV6_TSTAMP(c, 6);
+        WKV6_TSTAMP(ic, 6);
 
         if (tid == 0) {
             tc_fence_after_sync();
             // the state entering the next chunk is complete in shared memory: checkpoint it for the backward.
             // Its read is drained (bulk_wait_read) before the next chunk's first barrier, ahead of the rewrite.
-            if (a.ckpt != nullptr && c + 1 < nchunks) {
+            if (a.ckpt != nullptr && !a.reverse_state && c + 1 < nchunks) {
                 bulk_store(a.ckpt + ((size_t)blockIdx.x * nchunks + c + 1) * 4096, sSB, kTile);
                 bulk_commit();
             }
@@ -489,10 +499,10 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 umma_ss(tmY, dAM + 2 * kk, dV + so + 128 * kk, idKM, true);
             umma_commit(bar_mma2);
         }
-        WKV6_TSTAMP(c, 7);
-        if (!cta_wait(bar_mma2, c & 1, warp)) err = 3;
+        WKV6_TSTAMP(ic, 7);
+        if (!cta_wait(bar_mma2, ic & 1, warp)) err = 3;
         tc_fence_after_sync();
-        WKV6_TSTAMP(c, 8);
+        WKV6_TSTAMP(ic, 8);
 
         // ---- y epilogue: round to bf16 into the (now free) A tile, one TMA store per chunk
         {
@@ -510,13 +520,13 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         fence_proxy_async_smem();
         tc_fence_before_sync();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
-        WKV6_TSTAMP(c, 9);
+        WKV6_TSTAMP(ic, 9);
         if (tid == 0) {
             if (a.write_y) {
                 tma_store_3d(&tm_y, sAM, h * 64, c * kChunk, b);
                 bulk_commit();
             }
-            if (c + 2 < nchunks) { issue_loads(c + 2); ++loads_pending; }
+            if (ic + 2 < nchunks) { issue_loads(ic + 2); ++loads_pending; }
         }
     }
 
@@ -532,6 +542,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         }
         bulk_wait<0>();
     }
+    if (err == 0 && a.dec_out != nullptr && warp == 0)
+        *reinterpret_cast<float2 *>(a.dec_out + (size_t)blockIdx.x * 64 + 2 * lane) = dsum;
     if (err == 0 && a.s_out != nullptr) {
         const size_t so2 = (size_t)blockIdx.x * 4096;
 #pragma unroll

@@ -1,0 +1,154 @@
+"""WKV6 with the sequence split along T: inside one GPU (more independent work when there are few (batch, head)
+pairs) and across GPUs (each rank holds a contiguous T range; the N x N per-head states are carried rank to rank).
+
+A segment is summarised as an affine map of the state, S -> 2^dec * S + b (dec per key channel, b = the state the
+segment builds from zero).  Maps compose associatively, so every rank gathers all summaries (H*(N*N+N)*4 bytes per
+segment), runs the same exclusive scan and starts its segments from the right states; the backward does the mirror
+image for the reverse state.  The reference has no counterpart: its kernels cap T at a compile-time constant
+(rwkv_kernel/jax_kernel/rwkv_kernels.cu:351) and its only long-sequence mechanism is forward state chaining
+(rwkv_kernel/__init__.py:14-37).
+
+The numerical work is done by a *backend* (the CUDA library by default); the orchestration - reshaping, gathering,
+scanning, slicing - is backend-independent so that it can be exercised on CPU ranks with the oracle as backend.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class LibraryBackend:
+    """Chunked sm_100a kernels through the C ABI (bf16 r,k,v,w,gy; N = 64)."""
+
+    def __init__(self, head_size: int):
+        from . import _lib, ops
+        self.L, self.ops, self.N = _lib, ops, head_size
+
+    def _problem(self, x, u=None):
+        u = u if u is not None else torch.empty(0, dtype=torch.float32, device=x.device)
+        return self.ops.make_problem(x, u, self.N, x.dtype, self.L.VARIANT_CHUNK)
+
+    def _stream(self, x):
+        return ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+
+    def summary(self, x1, x2, w, reverse: bool):
+        Bn, T, C = x1.shape
+        H = C // self.N
+        state = torch.empty((Bn, H, self.N, self.N), dtype=torch.float32, device=x1.device)
+        dec = torch.empty((Bn, H, self.N), dtype=torch.float32, device=x1.device)
+        p = self._problem(x1)
+        ptr = self.ops._ptr
+        with torch.cuda.device(x1.device):
+            self.L.check(self.L.lib.wkv6_segment_summary(ctypes.byref(p), ptr(x1), ptr(x2), ptr(w), int(reverse), ptr(state),
+                                                         ptr(dec), self._stream(x1)))
+        return state, dec
+
+    def scan(self, B, H, G, dec, state, s0, reverse: bool):
+        out = torch.empty_like(state)
+        last = torch.empty((B, H, self.N, self.N), dtype=torch.float32, device=state.device)
+        ptr = self.ops._ptr
+        with torch.cuda.device(state.device):
+            self.L.check(self.L.lib.wkv6_state_scan(B, H, self.N, G, ptr(dec), ptr(state), ptr(s0), ptr(out), ptr(last),
+                                                    int(reverse), self._stream(state)))
+        return out, last
+
+    def forward(self, r, k, v, w, u, s_in, want_ckpt: bool):
+        y, _, ckpt = self.ops.forward_raw(r, k, v, w, u, self.N, s_in=s_in, want_ckpt=want_ckpt, variant=self.L.VARIANT_CHUNK)
+        return y, ckpt
+
+    def backward(self, r, k, v, w, u, gy, ckpt, ab_in):
+        Bn, T, C = r.shape
+        H = C // self.N
+        p = self.ops.make_problem(r, u, self.N, r.dtype, self.L.VARIANT_CHUNK)
+        g = [torch.empty_like(r) for _ in range(4)]
+        gu = torch.empty((Bn, H, self.N), dtype=torch.float32, device=r.device)
+        ptr = self.ops._ptr
+        with torch.cuda.device(r.device):
+            self.L.check(self.L.lib.wkv6_backward_seeded(ctypes.byref(p), ptr(r), ptr(k), ptr(v), ptr(w), ptr(u), ptr(gy),
+                                                         *(ptr(x) for x in g), ptr(gu), ptr(ckpt), ptr(ab_in), self._stream(r)))
+        return (*g, gu)
+
+
+def _split(x: torch.Tensor, G: int) -> torch.Tensor:
+    """[B, T, C] -> [B*G, T/G, C] (a view: segment g of batch row b becomes row b*G + g)."""
+    B, T, C = x.shape
+    assert T % G == 0, "T must be a multiple of the number of segments"
+    assert x.is_contiguous()
+    return x.view(B * G, T // G, C)
+
+
+def _gather_segments(x: torch.Tensor, B: int, G: int, group) -> torch.Tensor:
+    """Summaries [B*G, ...] of every rank -> [B*(R*G), ...] with the segments of rank 0 first along g."""
+    if group is None or dist.get_world_size(group) == 1:
+        return x
+    R = dist.get_world_size(group)
+    parts = [torch.empty_like(x) for _ in range(R)]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    allx = torch.stack(parts, 0).view(R, B, G, *x.shape[1:])          # [R, B, G, ...]
+    return allx.transpose(0, 1).reshape(B * R * G, *x.shape[1:])       # [B, R, G, ...] -> [B*R*G, ...]
+
+
+def _local_segments(x: torch.Tensor, B: int, G: int, group) -> torch.Tensor:
+    if group is None or dist.get_world_size(group) == 1:
+        return x
+    R, rank = dist.get_world_size(group), dist.get_rank(group)
+    return x.view(B, R, G, *x.shape[1:])[:, rank].reshape(B * G, *x.shape[1:]).contiguous()
+
+
+def segmented_forward(backend, r, k, v, w, u, segments: int, init_state: Optional[torch.Tensor] = None,
+                      want_ckpt: bool = False, group=None):
+    """Forward over local tensors [B, T_local, C].  Returns (y, state after the whole sequence, context for backward)."""
+    B, T, C = r.shape
+    G = segments
+    rs, ks, vs, ws = (_split(x, G) for x in (r, k, v, w))
+    state, dec = backend.summary(ks, vs, ws, False)
+    H = state.shape[1]
+    R = 1 if group is None else dist.get_world_size(group)
+    state_all, dec_all = _gather_segments(state, B, G, group), _gather_segments(dec, B, G, group)
+    s_in_all, last = backend.scan(B, H, R * G, dec_all, state_all, init_state, False)
+    s_in = _local_segments(s_in_all, B, G, group)
+    y, ckpt = backend.forward(rs, ks, vs, ws, u, s_in, want_ckpt)
+    ctx = dict(dec_all=dec_all, ckpt=ckpt, B=B, G=G, H=H, group=group)
+    return y.view(B, T, C), last, ctx
+
+
+def segmented_backward(backend, ctx, r, k, v, w, u, gy):
+    """Gradients for local tensors [B, T_local, C]; gu is summed over batch rows, segments and ranks."""
+    B, G, H, group = ctx["B"], ctx["G"], ctx["H"], ctx["group"]
+    T, C = r.shape[1], r.shape[2]
+    rs, ks, vs, ws, gs = (_split(x, G) for x in (r, k, v, w, gy))
+    astate, _ = backend.summary(rs, gs, ws, True)
+    R = 1 if group is None else dist.get_world_size(group)
+    astate_all = _gather_segments(astate, B, G, group)
+    a_in_all, _ = backend.scan(B, H, R * G, ctx["dec_all"], astate_all, None, True)
+    a_in = _local_segments(a_in_all, B, G, group)
+    gr, gk, gv, gw, gu_rows = backend.backward(rs, ks, vs, ws, u, gs, ctx["ckpt"], a_in)
+    gu = gu_rows.sum(0)
+    if R > 1:
+        dist.all_reduce(gu, op=dist.ReduceOp.SUM, group=group)
+    return gr.view(B, T, C), gk.view(B, T, C), gv.view(B, T, C), gw.view(B, T, C), gu
+
+
+class _SegmentedWKV6(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, r, k, v, w, u, backend, segments, group):
+        y, _, c = segmented_forward(backend, r, k, v, w, u, segments, want_ckpt=True, group=group)
+        ctx.save_for_backward(r, k, v, w, u)
+        ctx.c, ctx.backend = c, backend
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        r, k, v, w, u = ctx.saved_tensors
+        gr, gk, gv, gw, gu = segmented_backward(ctx.backend, ctx.c, r, k, v, w, u, gy.contiguous())
+        return gr, gk, gv, gw, gu.to(u.dtype).reshape(u.shape), None, None, None
+
+
+def wkv6_segmented(r, k, v, w, u, head_size: int, segments: int, group=None, backend=None):
+    """Differentiable WKV6 (zero initial state) with every local sequence cut into ``segments`` pieces; with
+    ``group`` the T axis is additionally sharded over the ranks of the group in rank order."""
+    backend = backend or LibraryBackend(head_size)
+    return _SegmentedWKV6.apply(r, k, v, w, u, backend, segments, group)

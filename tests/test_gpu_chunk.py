@@ -150,3 +150,41 @@ def test_backward_bit_identical_reruns(pkg):
     b = pkg.backward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], t["gy"], N, variant=pkg.VARIANT_CHUNK)
     for x, y in zip(a, b):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("B,T,H,G", [(1, 512, 2, 2), (2, 1024, 2, 4), (1, 2048, 1, 8)])
+def test_segmented_matches_unsplit(pkg, B, T, H, G):
+    """Sequences cut into G segments along T (summaries -> scan -> seeded kernels) against the one-piece kernels."""
+    from star_rwkv6_b200 import segments as seg
+    d = O.make_inputs(B, T, H, N, seed=81 + G)
+    t = dev_inputs(d)
+    be = seg.LibraryBackend(N)
+    y, last, ctx = seg.segmented_forward(be, t["r"], t["k"], t["v"], t["w"], t["u"], G, want_ckpt=True)
+    g = seg.segmented_backward(be, ctx, t["r"], t["k"], t["v"], t["w"], t["u"], t["gy"])
+    torch.cuda.synchronize()
+    assert status(pkg) == 0
+    dr = rounded(d, torch.bfloat16)
+    yo, so = c_oracle.fwd(dr["r"], dr["k"], dr["v"], dr["w"], dr["u"], N)
+    ref = c_oracle.bwd(dr["r"], dr["k"], dr["v"], dr["w"], dr["u"], dr["gy"], N)
+    assert scaled_err(np_(y), yo) <= TOL_BF16
+    assert scaled_err(np_(last), so) <= TOL_BF16
+    for name, got, want in zip(("gr", "gk", "gv", "gw"), g[:4], ref[:4]):
+        assert scaled_err(np_(got), want) <= TOL_BF16, f"{name}: {scaled_err(np_(got), want):.3e}"
+    assert scaled_err(np_(g[4]), ref[4].sum(0)) <= TOL_BF16
+    # and against the unsplit kernels: same inputs, only the association of the state products differs
+    y1, s1, ck = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_state=True, want_ckpt=True, variant=pkg.VARIANT_CHUNK)
+    assert scaled_err(np_(y), np_(y1)) <= 1e-2
+    assert scaled_err(np_(last), np_(s1)) <= 5e-3
+
+
+def test_segmented_autograd(pkg):
+    from star_rwkv6_b200 import segments as seg
+    d = O.make_inputs(1, 1024, 2, N, seed=91)
+    t = {n: torch.tensor(d[n]).to(torch.bfloat16).cuda().requires_grad_(True) for n in ("r", "k", "v", "w")}
+    u = torch.tensor(d["u"]).cuda().requires_grad_(True)
+    y = seg.wkv6_segmented(t["r"], t["k"], t["v"], t["w"], u, N, segments=4)
+    y.backward(torch.tensor(d["gy"]).to(torch.bfloat16).cuda())
+    ref = oracle_all(rounded(d, torch.bfloat16), N)
+    got = dict(y=np_(y), gr=np_(t["r"].grad), gk=np_(t["k"].grad), gv=np_(t["v"].grad), gw=np_(t["w"].grad), gu=np_(u.grad))
+    for n in got:
+        assert scaled_err(got[n], ref[n]) <= TOL_BF16, n
