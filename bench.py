@@ -48,6 +48,11 @@ def parse():
     ap.add_argument("--H", type=int, default=32)
     ap.add_argument("--N", type=int, default=64)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--segments", type=int, default=0,
+                    help="cut every local sequence into this many segments along T (summaries + scan + seeded kernels); "
+                         "0 = automatic: 1 when a rank has at least 256 (batch, head) sequences, else enough to reach 256")
+    ap.add_argument("--tshard", action="store_true",
+                    help="shard T over the ranks (long sequences): states are carried rank to rank; implies weak=False")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-heads", type=int, default=0, help="(b,h) pairs in the CPU sample; 0 = auto")
@@ -204,10 +209,16 @@ def run_b200(a):
     from star_rwkv6_b200.rwkv_kernel.torch_rwkv_kernel import RWKVKernelOperator
 
     B, T, H, N = a.B, a.T, a.H, a.N
-    if a.scaling == "strong" and world > 1:
+    if a.tshard and world > 1:
+        assert T % world == 0
+        T = T // world                                            # each rank holds a contiguous T range
+    elif a.scaling == "strong" and world > 1:
         from star_rwkv6_b200 import sharding
         B, H = sharding.make_plan(a.B, a.H, world).local_shape()  # each rank generates its own shard directly
     C = H * N
+    if a.segments == 0:
+        from star_rwkv6_b200.segments import auto_segments
+        a.segments = auto_segments(B, T, H) if (a.dtype == "bf16" and N == 64 and a.variant != "seq") else 1
     xdt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
     variant = _lib.VARIANTS[a.variant]
 
@@ -231,13 +242,27 @@ def run_b200(a):
     resolved = pkg.ops.resolve_variant(devs[0]["r"], u, N, variant)
     vname = {1: "seq", 2: "chunk"}[resolved]
     launches_per_step = {"seq": 4, "chunk": 2}[vname]
+    segmented = a.segments > 1 or (a.tshard and world > 1)
+    if segmented:
+        from star_rwkv6_b200 import segments as seg
+        assert vname == "chunk", "sequence splitting uses the chunked kernels"
+        be = seg.LibraryBackend(N)
+        grp = dist.group.WORLD if (a.tshard and world > 1) else None
+        launches_per_step = 6  # summary + scan + kernel, forward and backward
 
-    def step(d):
-        y, _, ckpt = pkg.forward_raw(d["r"], d["k"], d["v"], d["w"], u, N, want_ckpt=True, variant=variant)
-        return y, ckpt
+        def step(d):
+            y, _, ctx = seg.segmented_forward(be, d["r"], d["k"], d["v"], d["w"], u, a.segments, want_ckpt=True, group=grp)
+            return y, ctx
 
-    def step_bwd(d, ckpt):
-        return pkg.backward_raw(d["r"], d["k"], d["v"], d["w"], u, d["gy"], N, ckpt=ckpt, variant=variant)
+        def step_bwd(d, ctx):
+            return seg.segmented_backward(be, ctx, d["r"], d["k"], d["v"], d["w"], u, d["gy"])
+    else:
+        def step(d):
+            y, _, ckpt = pkg.forward_raw(d["r"], d["k"], d["v"], d["w"], u, N, want_ckpt=True, variant=variant)
+            return y, ckpt
+
+        def step_bwd(d, ckpt):
+            return pkg.backward_raw(d["r"], d["k"], d["v"], d["w"], u, d["gy"], N, ckpt=ckpt, variant=variant)
 
     # clocks are sampled from the warm-up on: the timed region itself can be shorter than one sampling period
     sampler = ClockSampler(local) if rank == 0 else None
@@ -277,13 +302,13 @@ def run_b200(a):
         total_ms, fwd_ms, bwd_ms = t.tolist()
     ms_per_step = total_ms / a.steps
     tokens_per_step_global = B * T * world  # every rank processes B*T tokens of H heads
-    if a.scaling == "strong" and world > 1:
+    if (a.scaling == "strong" or a.tshard) and world > 1:
         tokens_per_step_global = a.B * a.T
     value = tokens_per_step_global / (ms_per_step * 1e-3) / 1e6
 
     # e2e: through the operator, host buffers, copies inside the timed region
     e2e = None
-    if not a.no_e2e:
+    if not a.no_e2e and not segmented:
         op = RWKVKernelOperator(N, T, variant=a.variant)
         ydt = xdt
         out_host = {n: torch.empty(B, T, C, dtype=ydt).pin_memory() for n in ("y", "gr", "gk", "gv", "gw")}
@@ -333,10 +358,13 @@ def run_b200(a):
         esz = 2 if a.dtype == "bf16" else 4
         elems = B * T * C
         bwd_bytes, fwd_bytes = 9 * esz * elems, 5 * esz * elems
+        # dram__bytes_read.sum + dram__bytes_write.sum per (token, channel) of the chunked backward, from the ncu
+        # capture summarised under profiles/ (it scales with the number of (batch, head) sequences)
+        traffic = 18.3 * elems if (vname == "chunk" and a.dtype == "bf16" and not segmented) else None
         achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
         roofline = {
             "bound": "hbm", "kernel": f"{vname} backward", "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+            "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
             "algorithmic_bytes_per_launch": bwd_bytes, "avg_ms": bwd_ms,
             "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
                         "algorithmic_bytes_per_launch": fwd_bytes, "avg_ms": fwd_ms},
@@ -346,12 +374,14 @@ def run_b200(a):
         cpu = None if a.no_cpu_baseline else cpu_baseline(a)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": a.scaling, "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if a.tshard else a.scaling, "vs_baseline": None,
             "dtype": "bf16" if a.dtype == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": workload_name(a), "per_gpu": f"B{B} T{T} H{H} N{N}", "variant": vname,
                        "u_dtype": "f32", "state": "f32",
                        "l2": "two rotating input sets of 671 MB each, larger than the 126 MB L2",
-                       "parallelism": f"{world} independent ranks over (batch, head), no collective"},
+                       "segments_per_sequence": a.segments,
+                       "parallelism": (f"T sharded over {world} ranks, states carried by all-gather + scan" if (a.tshard and world > 1)
+                                       else f"{world} independent ranks over (batch, head), no collective")},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
             "gpu_launches": launches_per_step * a.steps,
         }

@@ -20,10 +20,13 @@ from .. import _lib, ops
 
 
 class RWKVKernelOperator:
-    def __init__(self, head_size, max_sequence_length=None, variant="auto"):
+    def __init__(self, head_size, max_sequence_length=None, variant="auto", segments=1):
+        """``segments``: 1 = one kernel walks each (batch, head) sequence; an integer G > 1 or "auto" cuts every
+        sequence into G pieces along T that run concurrently (worth it when B*H is small; bf16, head size 64)."""
         self.head_size = int(head_size)
         self.max_sequence_length = max_sequence_length
         self.variant = _lib.VARIANTS[variant] if isinstance(variant, str) else int(variant)
+        self.segments = segments
 
     def __call__(self, r, k, v, w, u, return_state=False, init_state=None, state_map=None):
         B, T, C = r.shape
@@ -75,4 +78,11 @@ class RWKVKernelOperator:
             return ops.wkv6_with_state(r, k, v, w, u, self.head_size, init_state=init_state, state_map=state_map,
                                        variant=self.variant)
         assert init_state is None and state_map is None, "init_state / state_map need return_state=True"
+        G = self.segments
+        if G != 1 and r.dtype == torch.bfloat16 and self.head_size == 64 and self.variant != _lib.VARIANT_SEQ and r.is_contiguous():
+            from .. import segments as seg
+            if G == "auto":
+                G = seg.auto_segments(B, T, H)
+            if G > 1 and T % G == 0:
+                return seg.wkv6_segmented(r, k, v, w, u, self.head_size, segments=G), None
         return ops.wkv6(r, k, v, w, u, self.head_size, variant=self.variant), None

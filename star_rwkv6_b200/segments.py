@@ -72,6 +72,15 @@ class LibraryBackend:
         return (*g, gu)
 
 
+def auto_segments(B: int, T: int, H: int, target_sequences: int = 256, max_segments: int = 16, min_tokens: int = 256) -> int:
+    """Number of segments that brings B*H*G independent sequences to about two per SM (the kernels run two CTAs per
+    SM, one CTA per sequence): a power of two, dividing T, with at least ``min_tokens`` tokens per segment."""
+    G = 1
+    while (B * H * G < target_sequences and G < max_segments and T % (2 * G) == 0 and T // (2 * G) >= min_tokens):
+        G *= 2
+    return G
+
+
 def _split(x: torch.Tensor, G: int) -> torch.Tensor:
     """[B, T, C] -> [B*G, T/G, C] (a view: segment g of batch row b becomes row b*G + g)."""
     B, T, C = x.shape

@@ -188,3 +188,19 @@ def test_segmented_autograd(pkg):
     got = dict(y=np_(y), gr=np_(t["r"].grad), gk=np_(t["k"].grad), gv=np_(t["v"].grad), gw=np_(t["w"].grad), gu=np_(u.grad))
     for n in got:
         assert scaled_err(got[n], ref[n]) <= TOL_BF16, n
+
+
+def test_operator_auto_segments(pkg):
+    from star_rwkv6_b200.rwkv_kernel.torch_rwkv_kernel import RWKVKernelOperator
+    from star_rwkv6_b200.segments import auto_segments
+    assert auto_segments(8, 4096, 32) == 1 and auto_segments(1, 4096, 32) == 8 and auto_segments(1, 131072, 32) == 8
+    d = O.make_inputs(1, 2048, 2, N, seed=93)
+    op = RWKVKernelOperator(N, 2048, segments="auto")
+    t = {n: torch.tensor(d[n]).to(torch.bfloat16).cuda().requires_grad_(True) for n in ("r", "k", "v", "w")}
+    u = torch.tensor(d["u"]).cuda().requires_grad_(True)
+    y, _ = op(t["r"], t["k"], t["v"], t["w"], u)
+    y.backward(torch.tensor(d["gy"]).to(torch.bfloat16).cuda())
+    ref = oracle_all(rounded(d, torch.bfloat16), N)
+    got = dict(y=np_(y), gr=np_(t["r"].grad), gk=np_(t["k"].grad), gv=np_(t["v"].grad), gw=np_(t["w"].grad), gu=np_(u.grad))
+    for n in got:
+        assert scaled_err(got[n], ref[n]) <= TOL_BF16, n
