@@ -137,6 +137,16 @@ WKV6_API int wkv6_backward_static_scratch(const wkv6_problem *p, const void *r, 
 WKV6_API size_t wkv6_static_scratch_bytes(void);
 
 /*
+ * Decode step: the T == 1 case of the forward with state, as its own streaming kernel (one read and one write of
+ * the fp32 state [B,H,N,N], N == 64).  Replaces kernel_forward_state at T = 1
+ * (rwkv_kernel/jax_kernel/rwkv_kernels.cu:165-190).  s_in may be NULL (zero state) and may equal s_out (in-place
+ * update, the serving loop's case) as long as no s_map row is shared between batch rows.
+ */
+WKV6_API int wkv6_decode(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
+                         const void *u, void *y, const float *s_in, const int64_t *s_map, int32_t s_kinds,
+                         float *s_out, void *stream);
+
+/*
  * Sequence splitting along T (no counterpart in the reference, whose kernels cap T at a compile-time constant and
  * never split a sequence; BASELINE's long-sequence configuration asks for it).  A sequence cut into G segments is
  * handled as a batch of B*G shorter sequences (a dense [B, G*Tseg, C] tensor is a [B*G, Tseg, C] tensor) whose

@@ -20,7 +20,7 @@ VARIANTS = {"auto": VARIANT_AUTO, "seq": VARIANT_SEQ, "chunk": VARIANT_CHUNK}
 SYMBOLS = (
     "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
     "wkv6_backward", "wkv6_backward_workspace_bytes", "wkv6_backward_static_scratch", "wkv6_static_scratch_bytes",
-    "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
+    "wkv6_decode", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
     "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_descriptor", "wkv6_xla_target",
 )
 
@@ -68,6 +68,8 @@ def _load():
     lib.wkv6_backward_static_scratch.argtypes = [pp] + [vp] * 11 + [vp]
     lib.wkv6_static_scratch_bytes.restype = sz
     lib.wkv6_static_scratch_bytes.argtypes = []
+    lib.wkv6_decode.restype = ctypes.c_int
+    lib.wkv6_decode.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, i64p, i32, vp, vp]
     lib.wkv6_segment_summary.restype = ctypes.c_int
     lib.wkv6_segment_summary.argtypes = [pp, vp, vp, vp, ctypes.c_int, vp, vp, vp]
     lib.wkv6_state_scan.restype = ctypes.c_int

@@ -147,6 +147,29 @@ def backward_raw(r, k, v, w, u, gy, head_size: int, *, ckpt=None, variant: int =
     return gr, gk, gv, gw, gu
 
 
+def wkv6_decode(r, k, v, w, u, head_size: int, state=None, state_map=None, out_state=None):
+    """One decode step on [B,1,C] tensors with an fp32 state [kinds,H,64,64] (None = zero).  Returns (y, new state);
+    pass ``out_state=state`` for an in-place update (one state per batch row, no state_map)."""
+    _check_cuda(r, k, v, w, u, state, state_map, out_state)
+    B, T, C = r.shape
+    assert T == 1 and head_size == 64 and r.is_contiguous()
+    H = C // head_size
+    ydt = out_dtype(r.dtype)
+    p = make_problem(r, u, head_size, ydt, _lib.VARIANT_AUTO)
+    y = torch.empty((B, 1, C), dtype=ydt, device=r.device)
+    kinds = 0
+    if state is not None:
+        assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, 64, 64)
+        kinds = state.shape[0]
+    if out_state is None:
+        out_state = torch.empty((B, H, 64, 64), dtype=torch.float32, device=r.device)
+    assert out_state.dtype == torch.float32 and out_state.shape == (B, H, 64, 64) and out_state.is_contiguous()
+    with torch.cuda.device(r.device):
+        check(lib.wkv6_decode(ctypes.byref(p), _ptr(r), _ptr(k), _ptr(v), _ptr(w), _ptr(u), _ptr(y), _ptr(state),
+                              _ptr(state_map), kinds, _ptr(out_state), _stream(r.device)))
+    return y, out_state
+
+
 # ---- torch.library registration -----------------------------------------------------------------
 
 @torch.library.custom_op("wkv6_b200::forward", mutates_args=(), device_types="cuda")

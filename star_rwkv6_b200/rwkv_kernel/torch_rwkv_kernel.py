@@ -75,6 +75,10 @@ class RWKVKernelOperator:
                     assert bool((state_map >= 0).all()) and bool((state_map < n_state).all()), \
                         f"state_map values must lie in [0, {n_state})"
                     state_map = state_map.to(r.device).contiguous()
+            if (T == 1 and self.head_size == 64 and r.is_contiguous()
+                    and (init_state is None or init_state.dtype == torch.float32)):
+                with torch.no_grad():  # decode step: dedicated state-streaming kernel
+                    return ops.wkv6_decode(r, k, v, w, u, self.head_size, state=init_state, state_map=state_map)
             return ops.wkv6_with_state(r, k, v, w, u, self.head_size, init_state=init_state, state_map=state_map,
                                        variant=self.variant)
         assert init_state is None and state_map is None, "init_state / state_map need return_state=True"

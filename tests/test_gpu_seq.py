@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from helpers import TOL_BF16, TOL_F32, np_, oracle_all, rounded, scaled_err
+from oracle import c_oracle
 from oracle import wkv6_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -160,3 +161,30 @@ def test_errors(pkg):
     with pytest.raises(AssertionError):
         op(zc, zc, zc, zc, torch.zeros(1, 64).cuda(), return_state=True,
            init_state=torch.zeros(1, 1, 64, 64).cuda(), state_map=[3])
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+def test_decode_steps(pkg, dtype, tol):
+    """256-style decode loop in miniature: prefill with return_state, then single-token steps through the operator
+    (which routes T == 1 to the streaming decode kernel), against one oracle pass over the whole sequence."""
+    from star_rwkv6_b200.rwkv_kernel.torch_rwkv_kernel import RWKVKernelOperator
+    from star_rwkv6_b200 import ops
+    N, B, H, Tp, Td = 64, 3, 2, 40, 6
+    d = O.make_inputs(B, Tp + Td, H, N, seed=33)
+    dr = rounded(d, dtype, names=("r", "k", "v", "w")) if dtype != torch.float32 else d
+    t = {n: torch.tensor(d[n]).to(dtype).cuda() for n in ("r", "k", "v", "w")}
+    u = torch.tensor(d["u"]).cuda()
+    op = RWKVKernelOperator(N, Tp + Td)
+    y0, state = op(*(t[n][:, :Tp].contiguous() for n in "rkvw"), u, return_state=True)
+    state = state.float().contiguous()
+    ys = [y0]
+    for s in range(Td):
+        step = [t[n][:, Tp + s:Tp + s + 1].contiguous() for n in "rkvw"]
+        if s % 2 == 0:
+            y1, state = op(*step, u, return_state=True, init_state=state)
+        else:  # in-place form used by a serving loop
+            y1, state = ops.wkv6_decode(*step, u, N, state=state, out_state=state)
+        ys.append(y1)
+    yo, so = c_oracle.fwd(dr["r"], dr["k"], dr["v"], dr["w"], d["u"], N)
+    assert scaled_err(np_(torch.cat(ys, 1)), yo) <= tol
+    assert scaled_err(np_(state), so) <= tol
