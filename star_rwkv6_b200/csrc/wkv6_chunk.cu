@@ -21,7 +21,21 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
 }
 
 // [B][T][C] bf16 tensor seen as (channel, token, batch row); one box is 64 channels x 64 tokens, 128-byte swizzled.
+// The driver-API encoder needs a CUDA context current on the calling thread.  A thread that has made no runtime call
+// yet (an autograd worker, an XLA host thread) has none: bind the runtime's context of the current device once.
+static int ensure_context() {
+    static thread_local bool bound = false;
+    if (bound) return WKV6_OK;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaSetDevice(dev);
+    if (e != cudaSuccess) return cuda_fail(e, "binding the CUDA context to the calling thread");
+    bound = true;
+    return WKV6_OK;
+}
+
 static int make_map(CUtensorMap *m, const void *base, const wkv6_problem *p, const Dims &d, const char *what) {
+    if (int rc = ensure_context()) return rc;
     auto enc = get_encode();
     if (!enc) return fail(WKV6_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[3] = {(cuuint64_t)d.C, (cuuint64_t)p->T, (cuuint64_t)p->B};
