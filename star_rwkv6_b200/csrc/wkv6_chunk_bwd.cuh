@@ -242,7 +242,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     constexpr uint32_t idKK96 = umma_idesc_bf16(64, 96, false, false);
     constexpr uint32_t idKM = umma_idesc_bf16(64, 64, false, true);
     constexpr uint32_t idMM = umma_idesc_bf16(64, 64, true, true);
-    constexpr int goff[4] = {0, 0, 48, 80};  // first row of the distance-d copies inside sKD / sRD
+    // first row of the distance-d copies inside sKD / sRD (a function, not an array: an array lands in local memory)
+    auto goff = [](int d) { return d == 1 ? 0 : d == 2 ? 48 : 80; };
     // operand descriptors; a step of 16 along K is +2 (K-major operand) or +128 (MN-major operand)
     const uint64_t dR = umma_desc_sw128(smem_u32(sR)), dK = umma_desc_sw128(smem_u32(sK));
     const uint64_t dV = umma_desc_sw128(smem_u32(sV)), dW = umma_desc_sw128(smem_u32(sW));
@@ -372,10 +373,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                     *reinterpret_cast<__nv_bfloat162 *>(sKH + off) = __hmul2(kt, fkb);
 #pragma unroll
                     for (int d = 1; d <= 3; ++d) {
-                        if (w4 + d <= 3)  // k~ copy serving row block w4 + d: row goff[d] + t
-                            *reinterpret_cast<__nv_bfloat162 *>(sKD + goff[d] * 128 + off) = __hmul2(kt, mk[d - 1]);
-                        if (w4 - d >= 0)  // r~ copy serving column block w4 - d: row goff[d] + t - 16 d
-                            *reinterpret_cast<__nv_bfloat162 *>(sRD + (goff[d] - 16 * d) * 128 + off) = __hmul2(rt, mr[d - 1]);
+                        if (w4 + d <= 3)  // k~ copy serving row block w4 + d: row goff(d) + t
+                            *reinterpret_cast<__nv_bfloat162 *>(sKD + goff(d) * 128 + off) = __hmul2(kt, mk[d - 1]);
+                        if (w4 - d >= 0)  // r~ copy serving column block w4 - d: row goff(d) + t - 16 d
+                            *reinterpret_cast<__nv_bfloat162 *>(sRD + (goff(d) - 16 * d) * 128 + off) = __hmul2(rt, mr[d - 1]);
                     }
                 }
             }
@@ -453,7 +454,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 uint32_t o0 = 0, o1 = 0, o2 = 0, o3 = 0;
                 if (J <= I) {
                     const int dl = I - J;
-                    const uint32_t src = (dl == 0) ? (tmA + lo + 16 * J) : (tmAD + lo + goff[dl] + 16 * J);
+                    const uint32_t src = (dl == 0) ? (tmA + lo + 16 * J) : (tmAD + lo + goff(dl) + 16 * J);
                     uint32_t v8[8];
                     tmem_ld_16x256b_x2(src, v8);
                     tmem_wait_ld();
@@ -513,7 +514,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
 #pragma unroll
                     for (int J = 0; J <= I; ++J) {
                         // GR1 rows of block I += P[:, block J] k~copy(I-J)_J        (K = the 16 tokens of block J)
-                        const uint64_t kb = (I == J) ? dK + 128 * J : dKD + 8 * (goff[I - J] + 16 * J);
+                        const uint64_t kb = (I == J) ? dK + 128 * J : dKD + 8 * (goff(I - J) + 16 * J);
                         umma_ss_masked(tmP, dP + 2 * J, kb, idKM, J > 0, I);
                     }
             } else if (warp == 1) {
@@ -522,7 +523,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
 #pragma unroll
                     for (int I = J; I < 4; ++I) {
                         // GK1 rows of block J += P[block I, :]^T r~copy(I-J)_I      (K = the 16 tokens of block I)
-                        const uint64_t rb2 = (I == J) ? dR + 128 * I : dRD + 8 * (goff[I - J] + 16 * J);
+                        const uint64_t rb2 = (I == J) ? dR + 128 * I : dRD + 8 * (goff(I - J) + 16 * J);
                         umma_ss_masked(tmA, dP + 128 * I, rb2, idMM, I > J, J);
                     }
             } else {

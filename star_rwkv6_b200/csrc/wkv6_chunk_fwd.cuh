@@ -45,6 +45,9 @@ __device__ int g_chunk_status;
 __device__ long long g_chunk_timing[64][16];
 #define WKV6_TSTAMP(iter, k) \
     do { if (blockIdx.x == 0 && threadIdx.x == 0 && (iter) < 64) g_chunk_timing[(iter)][(k)] = clock64(); } while (0)
+#elif defined(WKV6_MARK)
+// phase markers in the generated PTX (for counting instructions per phase)
+#define WKV6_TSTAMP(iter, k) asm volatile("// WKV6_MARK " #k ::: "memory")
 #else
 #define WKV6_TSTAMP(iter, k) do { } while (0)
 #endif
@@ -297,15 +300,14 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         {
             float2 pre = make_float2(0.f, 0.f), post = make_float2(0.f, 0.f), head, tail;
             head = tail = make_float2(0.f, 0.f);
-            float2 totJ[4], headJ[4];
 #pragma unroll
             for (int J = 0; J < 4; ++J) {
-                headJ[J] = *reinterpret_cast<const float2 *>(&sHead[J * 64 + 2 * lane]);
+                const float2 hj = *reinterpret_cast<const float2 *>(&sHead[J * 64 + 2 * lane]);
                 const float2 tl = *reinterpret_cast<const float2 *>(&sTail[J * 64 + 2 * lane]);
-                totJ[J] = add2(headJ[J], tl);
-                if (J < w4) pre = add2(pre, totJ[J]);
-                if (J > w4) post = add2(post, totJ[J]);
-                if (J == w4) { head = headJ[J]; tail = tl; }
+                const float2 tj = add2(hj, tl);
+                if (J < w4) pre = add2(pre, tj);
+                if (J > w4) post = add2(post, tj);
+                if (J == w4) { head = hj; tail = tl; }
             }
             const float2 nbase = half ? make_float2(0.f, 0.f) : make_float2(-head.x, -head.y);
             const __nv_bfloat162 fR = to_bf2(make_float2(ex2f(head.x + pre.x), ex2f(head.y + pre.y)));
@@ -316,13 +318,13 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 float2 acc = tail;
 #pragma unroll
                 for (int dl = 1; dl <= 3; ++dl) {
+                    const int Jt = w4 + dl;  // the row block this copy serves
                     fD[dl - 1] = to_bf2(make_float2(0.f, 0.f));
-#pragma unroll
-                    for (int Jt = 1; Jt < 4; ++Jt) {
-                        if (Jt == w4 + dl) {
-                            fD[dl - 1] = to_bf2(make_float2(ex2f(acc.x + headJ[Jt].x), ex2f(acc.y + headJ[Jt].y)));
-                            acc = add2(acc, totJ[Jt]);
-                        }
+                    if (Jt <= 3) {
+                        const float2 hj = *reinterpret_cast<const float2 *>(&sHead[Jt * 64 + 2 * lane]);
+                        const float2 tl = *reinterpret_cast<const float2 *>(&sTail[Jt * 64 + 2 * lane]);
+                        fD[dl - 1] = to_bf2(make_float2(ex2f(acc.x + hj.x), ex2f(acc.y + hj.y)));
+                        acc = add2(acc, add2(hj, tl));
                     }
                 }
             }
