@@ -28,10 +28,6 @@
 
 namespace wkv6 {
 
-#ifndef WKV6_EXP
-#define WKV6_EXP 0  // experiment switches of instrumented builds; 0 in every product build
-#endif
-
 constexpr int kChunk = 64;
 constexpr int kTile = 8192;  // one [64 x 64] bf16 tile
 constexpr float kLog2e = 1.4426950408889634f;
@@ -83,7 +79,6 @@ struct ChunkFwdArgs {
 };
 
 __device__ __forceinline__ float ex2f(float x) {
-    if (WKV6_EXP & 2) return x * 0.5f + 1.0f;
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
@@ -96,7 +91,6 @@ __device__ __forceinline__ void st_bf2(uint8_t *p, float a, float b) {
 }
 // packed fp32 pairs (one issue slot for two lanes of work on sm_100)
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-    if (WKV6_EXP & 4) return make_float2(a.x * b.x, a.y * b.y);
     unsigned long long ra, rb, rc;
     asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
     asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
@@ -106,7 +100,6 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
     return c;
 }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) {
-    if (WKV6_EXP & 4) return make_float2(a.x + b.x, a.y + b.y);
     unsigned long long ra, rb, rc;
     asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
     asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
@@ -116,7 +109,6 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
     return c;
 }
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-    if (WKV6_EXP & 4) return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
     unsigned long long ra, rb, rc, rd;
     asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
     asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
@@ -352,16 +344,9 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 const __nv_bfloat162 er = to_bf2(make_float2(ex2f(ea.x), ex2f(ea.y)));
                 const __nv_bfloat162 ek = to_bf2(make_float2(ex2f(eb.x), ex2f(eb.y)));
                 const __nv_bfloat162 rb = rbv[tt], kb = kbv[tt];
-                if (WKV6_EXP & 16) { bon[tt] = 0.f; continue; }
-                if (WKV6_EXP & 8) {
-                    bon[tt] = 0.f;
-                } else {
-                    const float2 r2 = __bfloat1622float2(rb), k2 = __bfloat1622float2(kb);
-                    const float2 rk = mul2(r2, k2);
-                    bon[tt] = fmaf(rk.x, u2.x, rk.y * u2.y);
-                }
+                const float2 rk = mul2(__bfloat1622float2(rb), __bfloat1622float2(kb));
+                bon[tt] = fmaf(rk.x, u2.x, rk.y * u2.y);
                 const __nv_bfloat162 rt = __hmul2(rb, er), kt = __hmul2(kb, ek);
-                if (WKV6_EXP & 1) { bon[tt] += __low2float(__hmul2(rt, fR)) + __low2float(__hmul2(kt, fK)) + __low2float(__hmul2(kt, fD[0])) + __low2float(__hmul2(kt, fD[1])) + __low2float(__hmul2(kt, fD[2])); continue; }
                 *reinterpret_cast<__nv_bfloat162 *>(pt) = rt;                                   // r~
                 *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rt, fR);          // r^ (over w)
                 *reinterpret_cast<__nv_bfloat162 *>(pt + kTile) = kt;                           // k~ distance 0
@@ -371,7 +356,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 if (w4 == 0) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 80 * 128) = __hmul2(kt, fD[2]);   // rows [80,96)
             }
             // sum the bonus partials over the 32 channel pairs: 8 values across 32 lanes in 9 shuffles
-            if (!(WKV6_EXP & 8)) {
+            {
                 const bool up = (lane & 16) != 0;
 #pragma unroll
                 for (int i2 = 0; i2 < 4; ++i2) {
