@@ -17,7 +17,9 @@
 //   and commutes with bf16 rounding, and (2) the multipliers r~, k~ used here are the bf16-rounded operand values.
 // The exponentials are split around per-16-token-block reference points exactly as in the forward, so every
 // bf16 operand stays finite; block pairs (I, J) are separate MMAs whose output is restricted to the 16 rows of
-// one block with the disable-output-lane mask of tcgen05.mma.
+// one block with the disable-output-lane mask of tcgen05.mma.  A chunk whose total decay is mild in every channel
+// (kWideLimit2) uses one reference point, the middle of the chunk, for all four blocks: the block-pair factors are
+// then 1, the copies are skipped and GR1 / GK1 are two plain MMAs.
 //
 // All element-wise work is done in the accumulator-fragment layout of tcgen05.ld.16x256b: a thread owns tokens
 // {r0, r0+8} of block (warp & 3) and channels 8n+2q, 8n+2q+1 for four values of n ((warp >> 2) selects which
@@ -52,7 +54,8 @@ struct ChunkBwdSmem {
     static constexpr int oFRb = oOff + 1024;        // bf16  [4][64] 2^{ref(I)}            (reference relative to the chunk start)
     static constexpr int oFKb = oFRb + 512;         // bf16  [4][64] 2^{c_63 - ref(J)}
     static constexpr int oMKb = oFKb + 512;         // bf16  [6][64] 2^{ref(J+d) - ref(J)}: d=1: J=0..2, d=2: J=0..1, d=3: J=0
-    static constexpr int oU = oMKb + 768;           // float [64]    u of this head
+    static constexpr int oMK2 = oMKb + 768;         // bf16  [6][64] second part of the same factor when it is below 2^-120
+    static constexpr int oU = oMK2 + 768;           // float [64]    u of this head
     static constexpr int oDtot = oU + 256;          // float [64]    2^{c_63}
     static constexpr int oBonus = oDtot + 256;      // float [2][64]
     static constexpr int oVG = oBonus + 512;        // float [64]
@@ -160,6 +163,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     __nv_bfloat16 *sFRb = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oFRb);
     __nv_bfloat16 *sFKb = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oFKb);
     __nv_bfloat16 *sMKb = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oMKb);
+    __nv_bfloat16 *sMK2 = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oMK2);
     float *sU = reinterpret_cast<float *>(smem + SM::oU);
     float *sBonus = reinterpret_cast<float *>(smem + SM::oBonus), *sVG = reinterpret_cast<float *>(smem + SM::oVG);
     float *sXtot = reinterpret_cast<float *>(smem + SM::oXtot), *sBtot = reinterpret_cast<float *>(smem + SM::oBtot);
@@ -308,25 +312,38 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         WKV6_TSTAMP(it, 2);
 
         // ---- per (block, channel) factors, one pair per thread; the power-of-two ones are exact in bf16
+        bool wide;  // one reference point for the whole chunk
         {
             const int J = tid >> 6, i = tid & 63;
-            float base = 0.f, mybase = 0.f, ref[4];
+            float base = 0.f, mybase = 0.f, ref[4], cmid = 0.f;
 #pragma unroll
             for (int J2 = 0; J2 < 4; ++J2) {
                 ref[J2] = rintf(base + sHead[J2 * 64 + i]);  // integer: block-pair factors become powers of two
                 if (J2 == J) mybase = base;
                 base += sTot[J2 * 64 + i];
+                if (J2 == 1) cmid = rintf(base);
             }
+            wide = !__syncthreads_or(base < kWideLimit2);
             float myref = ref[0];
 #pragma unroll
             for (int J2 = 1; J2 < 4; ++J2) myref = (J2 == J) ? ref[J2] : myref;
+            if (wide) myref = cmid;
             sOff[J * 64 + i] = myref - mybase;
             sFRb[J * 64 + i] = __float2bfloat16_rn(pow2i(myref));
             sFKb[J * 64 + i] = __float2bfloat16_rn(ex2f(base - myref));
+            if (!wide) {
 #pragma unroll
-            for (int J2 = 1; J2 < 4; ++J2) {  // copy of block J serving row block J2 = J + d
-                const int d = J2 - J;
-                if (d >= 1) sMKb[((d == 1 ? 0 : d == 2 ? 3 : 5) + J) * 64 + i] = __float2bfloat16_rn(pow2i(ref[J2] - myref));
+                for (int J2 = 1; J2 < 4; ++J2) {  // copy of block J serving row block J2 = J + d
+                    const int d = J2 - J;
+                    if (d >= 1) {
+                        // 2^n, n = ref(J2) - ref(J) <= 0, can lie below the bf16 range while its product with an operand
+                        // of up to 2^115 does not: it is applied as two factors 2^max(n,-120) * 2^max(n+120,-120)
+                        const float n = ref[J2] - myref, n1 = fmaxf(n, -120.f);
+                        const int slot = ((d == 1 ? 0 : d == 2 ? 3 : 5) + J) * 64 + i;
+                        sMKb[slot] = __float2bfloat16_rn(pow2i(n1));
+                        sMK2[slot] = __float2bfloat16_rn(pow2i(fmaxf(n - n1, -120.f)));
+                    }
+                }
             }
             if (J == 0) sDtot[i] = ex2f(base);
         }
@@ -344,13 +361,20 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 const float2 uc = *reinterpret_cast<const float2 *>(&sU[col]);
                 const __nv_bfloat162 fkb = *reinterpret_cast<const __nv_bfloat162 *>(&sFKb[w4 * 64 + col]);
                 const __nv_bfloat162 frb = *reinterpret_cast<const __nv_bfloat162 *>(&sFRb[w4 * 64 + col]);
-                __nv_bfloat162 mk[3], mr[3];  // power-of-two factors of the copies for block distances 1..3
+                __nv_bfloat162 mk[3], mr[3], mk2[3], mr2[3];  // power-of-two factors of the copies for block distances 1..3
 #pragma unroll
                 for (int d = 1; d <= 3; ++d) {
                     const int row0 = (d == 1 ? 0 : d == 2 ? 3 : 5);
-                    mk[d - 1] = mr[d - 1] = frb;
-                    if (w4 + d <= 3) mk[d - 1] = *reinterpret_cast<const __nv_bfloat162 *>(&sMKb[(row0 + w4) * 64 + col]);
-                    if (w4 - d >= 0) mr[d - 1] = *reinterpret_cast<const __nv_bfloat162 *>(&sMKb[(row0 + w4 - d) * 64 + col]);
+                    mk[d - 1] = mr[d - 1] = mk2[d - 1] = mr2[d - 1] = frb;
+                    if (wide) continue;
+                    if (w4 + d <= 3) {
+                        mk[d - 1] = *reinterpret_cast<const __nv_bfloat162 *>(&sMKb[(row0 + w4) * 64 + col]);
+                        mk2[d - 1] = *reinterpret_cast<const __nv_bfloat162 *>(&sMK2[(row0 + w4) * 64 + col]);
+                    }
+                    if (w4 - d >= 0) {
+                        mr[d - 1] = *reinterpret_cast<const __nv_bfloat162 *>(&sMKb[(row0 + w4 - d) * 64 + col]);
+                        mr2[d - 1] = *reinterpret_cast<const __nv_bfloat162 *>(&sMK2[(row0 + w4 - d) * 64 + col]);
+                    }
                 }
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
@@ -373,10 +397,11 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                     *reinterpret_cast<__nv_bfloat162 *>(sKH + off) = __hmul2(kt, fkb);
 #pragma unroll
                     for (int d = 1; d <= 3; ++d) {
+                        if (wide) continue;
                         if (w4 + d <= 3)  // k~ copy serving row block w4 + d: row goff(d) + t
-                            *reinterpret_cast<__nv_bfloat162 *>(sKD + goff(d) * 128 + off) = __hmul2(kt, mk[d - 1]);
+                            *reinterpret_cast<__nv_bfloat162 *>(sKD + goff(d) * 128 + off) = __hmul2(__hmul2(kt, mk[d - 1]), mk2[d - 1]);
                         if (w4 - d >= 0)  // r~ copy serving column block w4 - d: row goff(d) + t - 16 d
-                            *reinterpret_cast<__nv_bfloat162 *>(sRD + (goff(d) - 16 * d) * 128 + off) = __hmul2(rt, mr[d - 1]);
+                            *reinterpret_cast<__nv_bfloat162 *>(sRD + (goff(d) - 16 * d) * 128 + off) = __hmul2(__hmul2(rt, mr[d - 1]), mr2[d - 1]);
                     }
                 }
             }
@@ -409,7 +434,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                     umma_ss(tmA, dR + 2 * kk, dK + 2 * kk, idKK, kk > 0);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)  // A, distances 1..3: r~ against the 96 rows of k~ copies
-                    umma_ss(tmAD, dR + 2 * kk, dKD + 2 * kk, idKK96, kk > 0);
+                    if (!wide) umma_ss(tmAD, dR + 2 * kk, dKD + 2 * kk, idKK96, kk > 0);
             } else if (warp == 2) {
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)  // GK2 = v Abar^T
@@ -454,7 +479,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 uint32_t o0 = 0, o1 = 0, o2 = 0, o3 = 0;
                 if (J <= I) {
                     const int dl = I - J;
-                    const uint32_t src = (dl == 0) ? (tmA + lo + 16 * J) : (tmAD + lo + goff(dl) + 16 * J);
+                    const uint32_t src = (dl == 0 || wide) ? (tmA + lo + 16 * J) : (tmAD + lo + goff(dl) + 16 * J);
                     uint32_t v8[8];
                     tmem_ld_16x256b_x2(src, v8);
                     tmem_wait_ld();
@@ -508,7 +533,17 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         // ---- MMA group 2, three issuing threads
         if (lane == 0 && warp < 3) {
             tc_fence_after_sync();
-            if (warp == 0) {
+            if (wide && warp < 2) {
+                if (warp == 0) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)  // GR1 = P k~   (P is zero on and above the diagonal)
+                        umma_ss(tmP, dP + 2 * kk, dK + 128 * kk, idKM, kk > 0);
+                } else {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)  // GK1 = P^T r~
+                        umma_ss(tmA, dP + 128 * kk, dR + 128 * kk, idMM, kk > 0);
+                }
+            } else if (warp == 0) {
 #pragma unroll
                 for (int I = 0; I < 4; ++I)
 #pragma unroll

@@ -12,7 +12,8 @@
 // Positive exponents span at most 8 steps; log-decays are clamped at -10 per step (a decay of e^-10, below
 // bf16 resolution of anything it multiplies), so every factor stays below e^80.  The block-pair factor is
 // folded into extra copies of k~ (one per block distance 1..3), all multiplied by the same r~ in one MMA;
-// the epilogue picks, per block pair, the columns of the matching copy.
+// the epilogue picks, per block pair, the columns of the matching copy.  Chunks with a mild total decay (see
+// kWideLimit2; the usual case) use the middle of the chunk as the single reference point and skip the copies.
 //
 // Tensor-memory map (256 columns, M = 64 accumulators occupy 16 lanes of each 32-lane quarter):
 //   lanes  0-15: cols [0,64) A for distance 0 | [64,128) y | [128,192) K^T V (state increment)
@@ -32,6 +33,10 @@ constexpr int kChunk = 64;
 constexpr int kTile = 8192;  // one [64 x 64] bf16 tile
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMinLogDecay2 = -10.0f * 1.4426950408889634f;  // clamp of the per-step log2 decay
+// A chunk whose total log2 decay stays above this limit in every channel takes one reference point for the whole
+// chunk (its middle) instead of one per 16-token block: every factor stays below 2^96, and the copies of k~ / r~
+// for the block distances 1..3 are not needed.
+constexpr float kWideLimit2 = -96.0f;
 
 // device-side error word: 0 = fine, otherwise the code of the wait that ran out
 __device__ int g_chunk_status;
@@ -264,6 +269,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         uint8_t *const tbase = sR + (16 * w4 + 8 * half) * 128 + ((lane & 3) << 2);
         const uint32_t lane_chunk = (uint32_t)(lane >> 2);
         const bool full_chunk = (c + 1) * kChunk <= a.T;
+        bool wide;  // single reference point for this chunk (the same value in every warp)
         float2 x[8];
         {
             float2 cs = make_float2(0.f, 0.f);
@@ -290,8 +296,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         // running sums of the second half are already relative to it and those of the first half need only -head.
         // The scaling itself runs on packed bf16 pairs: r and k are exact bf16 inputs, factors are rounded to bf16.
         {
-            float2 pre = make_float2(0.f, 0.f), post = make_float2(0.f, 0.f), head, tail;
-            head = tail = make_float2(0.f, 0.f);
+            float2 pre = make_float2(0.f, 0.f), post = make_float2(0.f, 0.f), head, tail, mid;
+            head = tail = mid = make_float2(0.f, 0.f);
 #pragma unroll
             for (int J = 0; J < 4; ++J) {
                 const float2 hj = *reinterpret_cast<const float2 *>(&sHead[J * 64 + 2 * lane]);
@@ -300,28 +306,36 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 if (J < w4) pre = add2(pre, tj);
                 if (J > w4) post = add2(post, tj);
                 if (J == w4) { head = hj; tail = tl; }
+                if (J < 2) mid = add2(mid, tj);
             }
-            const float2 nbase = half ? make_float2(0.f, 0.f) : make_float2(-head.x, -head.y);
-            const __nv_bfloat162 fR = to_bf2(make_float2(ex2f(head.x + pre.x), ex2f(head.y + pre.y)));
-            const __nv_bfloat162 fK = to_bf2(make_float2(ex2f(tail.x + post.x), ex2f(tail.y + post.y)));
+            const float2 all = add2(add2(head, tail), add2(pre, post));  // log2 decay of the whole chunk
+            wide = !__any_sync(0xffffffffu, fminf(all.x, all.y) < kWideLimit2);  // a warp sees all 64 channels
+            // reference point relative to the chunk start: the block's 8th token, or the chunk's 32nd
+            const float2 ref = wide ? mid : add2(pre, head);
+            const float2 gstart = half ? add2(pre, head) : pre;  // running sum before this thread's first token
+            const float2 nbase = make_float2(gstart.x - ref.x, gstart.y - ref.y);
+            const __nv_bfloat162 fR = to_bf2(make_float2(ex2f(ref.x), ex2f(ref.y)));
+            const __nv_bfloat162 fK = to_bf2(make_float2(ex2f(all.x - ref.x), ex2f(all.y - ref.y)));
             // factors of the k~ copies for block distances 1..3 (only those with w4 + delta <= 3 exist)
-            __nv_bfloat162 fD[3];
-            {
+            // (a factor can lie below the bf16 range while its product with k~ <= 2^115 does not: it is applied in two parts)
+            __nv_bfloat162 fD[3], fE[3];
+            fD[0] = fD[1] = fD[2] = fE[0] = fE[1] = fE[2] = to_bf2(make_float2(0.f, 0.f));
+            if (!wide) {
                 float2 acc = tail;
 #pragma unroll
                 for (int dl = 1; dl <= 3; ++dl) {
                     const int Jt = w4 + dl;  // the row block this copy serves
-                    fD[dl - 1] = to_bf2(make_float2(0.f, 0.f));
                     if (Jt <= 3) {
                         const float2 hj = *reinterpret_cast<const float2 *>(&sHead[Jt * 64 + 2 * lane]);
                         const float2 tl = *reinterpret_cast<const float2 *>(&sTail[Jt * 64 + 2 * lane]);
-                        fD[dl - 1] = to_bf2(make_float2(ex2f(acc.x + hj.x), ex2f(acc.y + hj.y)));
+                        const float2 n = add2(acc, hj), n1 = make_float2(fmaxf(n.x, -120.f), fmaxf(n.y, -120.f));
+                        fD[dl - 1] = to_bf2(make_float2(ex2f(n1.x), ex2f(n1.y)));
+                        fE[dl - 1] = to_bf2(make_float2(ex2f(fmaxf(n.x - n1.x, -120.f)), ex2f(fmaxf(n.y - n1.y, -120.f))));
                         acc = add2(acc, add2(hj, tl));
                     }
                 }
             }
             if (warp == 0) {
-                const float2 all = make_float2(head.x + tail.x + post.x, head.y + tail.y + post.y);
                 *reinterpret_cast<float2 *>(&sDtot[2 * lane]) = make_float2(ex2f(all.x), ex2f(all.y));
                 dsum = add2(dsum, all);
             }
@@ -351,9 +365,11 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rt, fR);          // r^ (over w)
                 *reinterpret_cast<__nv_bfloat162 *>(pt + kTile) = kt;                           // k~ distance 0
                 *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(kt, fK);                // k^
-                if (w4 <= 2) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo) = __hmul2(kt, fD[0]);              // rows [0,48)
-                if (w4 <= 1) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 48 * 128) = __hmul2(kt, fD[1]);   // rows [48,80)
-                if (w4 == 0) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 80 * 128) = __hmul2(kt, fD[2]);   // rows [80,96)
+                if (!wide) {
+                    if (w4 <= 2) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo) = __hmul2(__hmul2(kt, fD[0]), fE[0]);              // rows [0,48)
+                    if (w4 <= 1) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 48 * 128) = __hmul2(__hmul2(kt, fD[1]), fE[1]);   // rows [48,80)
+                    if (w4 == 0) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 80 * 128) = __hmul2(__hmul2(kt, fD[2]), fE[2]);   // rows [80,96)
+                }
             }
             // sum the bonus partials over the 32 channel pairs: 8 values across 32 lanes in 9 shuffles
             {
@@ -399,7 +415,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 umma_ss(tmA0, dR + so + 2 * kk, dK + so + 2 * kk, idKK, kk > 0);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // A (distances 1..3) = r~ [k~ copies]^T
-                umma_ss(tmAD, dR + so + 2 * kk, dKD + 2 * kk, idKK96, kk > 0);
+                if (!wide) umma_ss(tmAD, dR + so + 2 * kk, dKD + 2 * kk, idKK96, kk > 0);
             umma_commit(bar_mma1);
         } else if (tid == 32) {
             tc_fence_after_sync();
@@ -428,8 +444,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 uint32_t o0 = 0, o1 = 0, o2 = 0, o3 = 0;  // (row ta: cols 2q,2q+1 | 8+2q,..) and the same for row ta+8
                 if (J <= I) {
                     const int dl = I - J;
-                    const uint32_t src = (dl == 0) ? (tmA0 + wl + 16 * J)
-                                                   : (tmAD + wl + (dl == 1 ? 16 * J : dl == 2 ? 48 + 16 * J : 80));
+                    const uint32_t src = (dl == 0 || wide) ? (tmA0 + wl + 16 * J)
+                                                           : (tmAD + wl + (dl == 1 ? 16 * J : dl == 2 ? 48 + 16 * J : 80));
                     uint32_t v8[8];
                     tmem_ld_16x256b_x2(src, v8);
                     tmem_wait_ld();
