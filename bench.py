@@ -241,14 +241,14 @@ def run_b200(a):
 
     resolved = pkg.ops.resolve_variant(devs[0]["r"], u, N, variant)
     vname = {1: "seq", 2: "chunk"}[resolved]
-    launches_per_step = {"seq": 4, "chunk": 2}[vname]
+    launches_per_step = {"seq": 4, "chunk": 3}[vname]  # chunk: forward, fast backward, general backward (exits at once when nothing is flagged)
     segmented = a.segments > 1 or (a.tshard and world > 1)
     if segmented:
         from star_rwkv6_b200 import segments as seg
         assert vname == "chunk", "sequence splitting uses the chunked kernels"
         be = seg.LibraryBackend(N)
         grp = dist.group.WORLD if (a.tshard and world > 1) else None
-        launches_per_step = 6  # summary + scan + kernel, forward and backward
+        launches_per_step = 7  # summary + scan + kernel(s), forward and backward
 
         def step(d):
             y, _, ctx = seg.segmented_forward(be, d["r"], d["k"], d["v"], d["w"], u, a.segments, want_ckpt=True, group=grp)

@@ -103,7 +103,10 @@ WKV6_API size_t wkv6_ckpt_bytes(const wkv6_problem *p);
  * Every element of gr, gk, gv, gw, gu is written.
  *   ckpt      : the buffer a forward of the same problem filled, or NULL (then the backward rebuilds it
  *               inside the workspace)
- *   workspace : wkv6_backward_workspace_bytes(p, ckpt != NULL) bytes of device scratch (may be NULL when 0)
+ *   workspace : wkv6_backward_workspace_bytes(p, ckpt != NULL) bytes of device scratch (may be NULL when 0).
+ *               The chunked variant keeps one word per sequence there, with which its fast kernel (one decay
+ *               reference point per chunk) hands the sequences it cannot finish to the general kernel; with a
+ *               ckpt buffer but no workspace the call still succeeds, through the general kernel alone, slower.
  */
 WKV6_API int wkv6_backward(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
                   const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu,
@@ -159,7 +162,8 @@ WKV6_API int wkv6_decode(const wkv6_problem *p, const void *r, const void *k, co
  *      last_out (optional, [B,H,N,N]) = state after the last segment.  Across GPUs the summaries of all ranks are
  *      gathered (they are small: H*(N*N+N)*4 bytes per segment) and every rank runs the same scan.
  *   3. wkv6_forward on the [B*G, Tseg, C] problem with s_in = the scanned states (and a ckpt buffer), and
- *      wkv6_backward_seeded with ab_in = the scanned reverse states [B*G,H,N,N] fp32 and that ckpt buffer.
+ *      wkv6_backward_seeded with ab_in = the scanned reverse states [B*G,H,N,N] fp32, that ckpt buffer and a
+ *      workspace of wkv6_backward_workspace_bytes(p, 1) bytes.
  * Chunked variant only (N == 64, bf16 r,k,v,w,y).
  */
 WKV6_API int wkv6_segment_summary(const wkv6_problem *p, const void *x1, const void *x2, const void *w, int reverse,
@@ -168,7 +172,8 @@ WKV6_API int wkv6_state_scan(int32_t B, int32_t H, int32_t N, int32_t G, const f
                              const float *s0, float *state_in_out, float *last_out, int reverse, void *stream);
 WKV6_API int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
                                   const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu,
-                                  const void *ckpt, const float *ab_in, void *stream);
+                                  const void *ckpt, const float *ab_in, void *workspace, size_t workspace_bytes,
+                                  void *stream);
 
 /*
  * XLA legacy custom-call surface.  The library also exports the C++ symbols gpu_ops::rwkv_forward_fn,

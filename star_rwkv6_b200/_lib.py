@@ -75,7 +75,7 @@ def _load():
     lib.wkv6_state_scan.restype = ctypes.c_int
     lib.wkv6_state_scan.argtypes = [i32, i32, i32, i32, vp, vp, vp, vp, vp, ctypes.c_int, vp]
     lib.wkv6_backward_seeded.restype = ctypes.c_int
-    lib.wkv6_backward_seeded.argtypes = [pp] + [vp] * 11 + [vp, vp, vp]
+    lib.wkv6_backward_seeded.argtypes = [pp] + [vp] * 11 + [vp, vp, vp, sz, vp]
     for name in ("wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state"):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int

@@ -173,7 +173,7 @@ int wkv6_state_scan(int32_t B, int32_t H, int32_t N, int32_t G, const float *dec
 
 int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w, const void *u,
                          const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu, const void *ckpt,
-                         const float *ab_in, void *stream) {
+                         const float *ab_in, void *workspace, size_t workspace_bytes, void *stream) {
     Dims d;
     int rc = validate(p, &d);
     if (rc) return rc;
@@ -183,7 +183,9 @@ int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const void *k, co
     WKV6_CHECK_PTR(r); WKV6_CHECK_PTR(k); WKV6_CHECK_PTR(v); WKV6_CHECK_PTR(w); WKV6_CHECK_PTR(gy);
     WKV6_CHECK_PTR(gr); WKV6_CHECK_PTR(gk); WKV6_CHECK_PTR(gv); WKV6_CHECK_PTR(gw);
     if (u == nullptr || gu == nullptr) return fail(WKV6_ERR_INVALID, "u or gu is NULL");
-    return chunk_backward_seeded(p, d, r, k, v, w, u, gy, gr, gk, gv, gw, gu, ckpt, ab_in, nullptr, 0,
+    if (workspace != nullptr && reinterpret_cast<uintptr_t>(workspace) % 16)
+        return fail(WKV6_ERR_INVALID, "workspace is not 16-byte aligned");
+    return chunk_backward_seeded(p, d, r, k, v, w, u, gy, gr, gk, gv, gw, gu, ckpt, ab_in, workspace, workspace_bytes,
                                  static_cast<cudaStream_t>(stream));
 }
 

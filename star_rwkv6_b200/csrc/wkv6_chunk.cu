@@ -3,6 +3,7 @@
 #include <cudaTypedefs.h>
 
 #include "wkv6_chunk_bwd.cuh"
+#include "wkv6_chunk_bwd_wide.cuh"
 #include "wkv6_chunk_fwd.cuh"
 #include "wkv6_internal.h"
 
@@ -80,10 +81,12 @@ int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const voi
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_fwd_kernel launch");
 }
 
-// Without a checkpoint buffer from the forward, the backward first rebuilds the chunk-start states with the
-// forward kernel (its y output suppressed) inside the workspace.
+// Workspace of the backward: one word per sequence for the hand-over between the fast and the general kernel, then,
+// without a checkpoint buffer from the forward, room for the chunk-start states, which the backward first rebuilds
+// with the forward kernel (its y output suppressed).
+static size_t flag_bytes(const wkv6_problem *p) { return (((size_t)p->B * p->H * sizeof(int)) + 255) & ~(size_t)255; }
 size_t chunk_backward_workspace(const wkv6_problem *p, const Dims &, int have_ckpt) {
-    return have_ckpt ? 0 : chunk_ckpt_bytes(p);
+    return flag_bytes(p) + (have_ckpt ? 0 : chunk_ckpt_bytes(p));
 }
 
 int chunk_backward(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v, const void *w,
@@ -96,12 +99,15 @@ int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, c
                           const void *w, const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw,
                           void *gu, const void *ckpt, const float *ab_in, void *ws, size_t ws_bytes, cudaStream_t st) {
     int rc;
+    // A caller that passes no workspace although it holds the checkpoints still gets a result: from the general kernel alone.
+    int *flags = (ws != nullptr && ws_bytes >= flag_bytes(p)) ? static_cast<int *>(ws) : nullptr;
     if (ckpt == nullptr) {
-        const size_t need = chunk_ckpt_bytes(p);
+        const size_t need = flag_bytes(p) + chunk_ckpt_bytes(p);
         if (ws == nullptr || ws_bytes < need)
             return fail(WKV6_ERR_WORKSPACE, "backward workspace: need %zu bytes, got %zu", need, ws ? ws_bytes : (size_t)0);
-        if ((rc = chunk_forward(p, d, r, k, v, w, u, nullptr, nullptr, nullptr, 0, nullptr, ws, st))) return rc;
-        ckpt = ws;
+        void *area = static_cast<uint8_t *>(ws) + flag_bytes(p);
+        if ((rc = chunk_forward(p, d, r, k, v, w, u, nullptr, nullptr, nullptr, 0, nullptr, area, st))) return rc;
+        ckpt = area;
     }
     CUtensorMap mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw;
     if ((rc = make_map(&mr, r, p, d, "r"))) return rc;
@@ -117,8 +123,16 @@ int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, c
     a.u = u; a.u_dtype = p->u_dtype; a.gu = gu; a.gu_dtype = p->gu_dtype;
     a.ckpt = static_cast<const __nv_bfloat16 *>(ckpt); a.B = p->B; a.T = p->T; a.H = p->H;
     a.ab_in = ab_in; a.zero_init = (ab_in == nullptr);  // a seeded call is one segment of a longer sequence
-    cudaError_t e = cudaFuncSetAttribute(chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         ChunkBwdSmem::kAlloc);
+    a.flags = flags;
+    cudaError_t e;
+    if (flags != nullptr) {  // the fast kernel first; it marks the sequences it has to leave to the general one
+        e = cudaFuncSetAttribute(chunk_bwd_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideBwdSmem::kAlloc);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_wide_kernel)");
+        chunk_bwd_wide_kernel<<<p->B * p->H, 256, WideBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "chunk_bwd_wide_kernel launch");
+    }
+    e = cudaFuncSetAttribute(chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ChunkBwdSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_kernel)");
     chunk_bwd_kernel<<<p->B * p->H, 256, ChunkBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
     e = cudaGetLastError();

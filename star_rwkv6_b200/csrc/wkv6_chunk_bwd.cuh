@@ -76,6 +76,9 @@ struct ChunkBwdArgs {
     const float *ab_in;  // optional [B*H][64][64]: reverse state entering at the end of the sequence (zero if NULL)
     bool zero_init;      // the forward started from a zero state: gw at t = 0 is exactly zero
     int B, T, H;
+    // Hand-over between the two backward kernels, one word per (batch, head) sequence: chunk_bwd_wide_kernel writes
+    // 1 for a sequence it abandoned (0 otherwise); chunk_bwd_kernel given the same array skips sequences marked 0.
+    int *flags;
 };
 
 // D[tmem] (+)= A * B restricted to the TMEM lanes whose mask bit is 0.
@@ -155,6 +158,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         if (threadIdx.x == 0) atomicExch(&g_chunk_status, 50);
         return;
     }
+    if (a.flags != nullptr && a.flags[blockIdx.x] == 0) return;  // the fast kernel has completed this sequence
     uint8_t *sR = smem + SM::oR, *sK = smem + SM::oK, *sV = smem + SM::oV, *sW = smem + SM::oW, *sG = smem + SM::oG;
     uint8_t *sS = smem + SM::oS, *sKH = smem + SM::oKH, *sKD = smem + SM::oKD, *sRD = smem + SM::oRD;
     uint8_t *sP = smem + SM::oP, *sAM = smem + SM::oAM, *sAB = smem + SM::oAB;

@@ -66,9 +66,12 @@ class LibraryBackend:
         g = [torch.empty_like(r) for _ in range(4)]
         gu = torch.empty((Bn, H, self.N), dtype=torch.float32, device=r.device)
         ptr = self.ops._ptr
+        nbytes = self.L.lib.wkv6_backward_workspace_bytes(ctypes.byref(p), 1)
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=r.device) if nbytes else None
         with torch.cuda.device(r.device):
             self.L.check(self.L.lib.wkv6_backward_seeded(ctypes.byref(p), ptr(r), ptr(k), ptr(v), ptr(w), ptr(u), ptr(gy),
-                                                         *(ptr(x) for x in g), ptr(gu), ptr(ckpt), ptr(ab_in), self._stream(r)))
+                                                         *(ptr(x) for x in g), ptr(gu), ptr(ckpt), ptr(ab_in), ptr(ws),
+                                                         nbytes, self._stream(r)))
         return (*g, gu)
 
 
