@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     __syncthreads();
     tc_fence_after_sync();
 
-    // thread 0: loads in flight per barrier and the phase parity their completion will have
+    // copy thread: loads in flight per barrier and the phase parity their completion will have
     bool pend_w = false, pend_rk = false, pend_late = false;
     uint32_t par_early = 0, par_rk = 0;
     auto issue_early = [&](int c) {  // tiles that are dead once the second MMA group has completed
@@ -198,7 +198,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         tma_load_3d(sK, &tm_k, bar_rk, h * 64, c * kChunk, b);
         pend_rk = true;
     };
-    if (tid == 0) { issue_early(nchunks - 1); issue_rk(nchunks - 1); }
+    // Copies are issued by one thread of warp 4, so that warps 0-3, which poll the barriers and issue the MMAs, never
+    // queue behind them.
+    const bool copy_thread = (tid == 128);
+    if (copy_thread) { issue_early(nchunks - 1); issue_rk(nchunks - 1); }
 
     constexpr uint32_t idKK = umma_idesc_bf16(64, 64, false, false);
     constexpr uint32_t idKM = umma_idesc_bf16(64, 64, false, true);
@@ -216,7 +219,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         const int c = nchunks - 1 - it;
         WKV6_TSTAMP(it, 0);
         if (!cta_wait(bar_w, it & 1, warp)) err = 1;
-        if (tid == 0) pend_w = false;
+        if (copy_thread) pend_w = false;
         WKV6_TSTAMP(it, 1);
 
         // ---- per-step log2 decays and their running sums inside the block (fragment layout)
@@ -259,7 +262,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             }
         }
         tmem_wait_st();
-        if (tid == 0) bulk_wait_read<0>();  // the previous chunk's output tiles have left shared memory
+        if (copy_thread) bulk_wait_read<0>();  // the previous chunk's output tiles have left shared memory
         if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
         WKV6_TSTAMP(it, 2);
 
@@ -286,7 +289,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             bool ok = true;
             if (warp == 0) ok = mbar_wait(bar_rk, it & 1);  // r, k have landed (long ago, normally)
             if (!__syncthreads_and(ok && err == 0)) { err = err ? err : 5; break; }
-            if (tid == 0) pend_rk = false;
+            if (copy_thread) pend_rk = false;
         }
         WKV6_TSTAMP(it, 3);
 
@@ -333,7 +336,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             bool ok = true;
             if (warp == 0) ok = mbar_wait(bar_late, it & 1);  // v, gy, S_in have landed (long ago, normally)
             if (!__syncthreads_and(ok && err == 0)) { err = err ? err : 4; break; }
-            if (tid == 0) pend_late = false;
+            if (copy_thread) pend_late = false;
         }
         WKV6_TSTAMP(it, 4);
 
@@ -472,7 +475,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         tc_fence_after_sync();
         WKV6_TSTAMP(it, 9);
         // w, v, gy and the state tile are dead once the second MMA group has completed: fetch the next chunk's now
-        if (tid == 0 && c > 0 && err == 0) issue_early(c - 1);
+        if (copy_thread && c > 0 && err == 0) issue_early(c - 1);
 
         // ---- epilogue 2: gr, gk, gv, gw, one 8-column repetition at a time
         float loc[16];  // G minus its per-channel base (see below)
@@ -558,7 +561,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         __syncthreads();
         WKV6_TSTAMP(it, 10);
         // every thread has read its raw r, k: fetch the next chunk's
-        if (tid == 0 && c > 0 && err == 0) issue_rk(c - 1);
+        if (copy_thread && c > 0 && err == 0) issue_rk(c - 1);
         // G_t = e^{c_63} <S_in, Abar> + sum_all b + sum_{later blocks} q + (suffix_incl(q) - a)_t ;  gw = -exp(w) G
         uint32_t lwst2[8];
         tmem_ld_16x256b_x2(tmStash, lwst2);
@@ -587,7 +590,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         fence_proxy_async_smem();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
         WKV6_TSTAMP(it, 11);
-        if (tid == 0) {
+        if (copy_thread) {
             tma_store_3d(&tm_gr, sP, h * 64, c * kChunk, b);
             tma_store_3d(&tm_gk, sAM, h * 64, c * kChunk, b);
             tma_store_3d(&tm_gv, sKT, h * 64, c * kChunk, b);
@@ -597,7 +600,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     }
 
     // ---- unwind: wait (bounded) for loads still aimed at this CTA's shared memory, drain the stores, report
-    if (tid == 0) {
+    if (copy_thread) {
         if (err != 0 || bail) {
             if (pend_w) mbar_wait(bar_w, par_early);
             if (pend_late) mbar_wait(bar_late, par_early);

@@ -230,7 +230,10 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         tma_load_3d(base + 2 * kTile, &tm_v, &bar_full[st], h * 64, c * kChunk, b);
         tma_load_3d(base + 3 * kTile, &tm_w, &bar_full[st], h * 64, c * kChunk, b);
     };
-    if (tid == 0) {
+    // Copies (TMA loads and stores, checkpoint stores) are issued by one thread of warp 1, so that warp 0, which
+    // polls the barriers for the whole CTA and issues MMAs, never queues behind them.
+    const bool copy_thread = (tid == 32);
+    if (copy_thread) {
         issue_loads(0);
         if (nchunks > 1) issue_loads(1);
         if (a.ckpt != nullptr) {  // state at the start of chunk 0, already in operand layout
@@ -251,7 +254,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     const uint64_t dAM = umma_desc_sw128(smem_u32(sAM)), dSB = umma_desc_sw128(smem_u32(sSB));
 
     int err = 0;
-    int loads_pending = (nchunks > 1) ? 2 : 1;  // meaningful on thread 0 only
+    int loads_pending = (nchunks > 1) ? 2 : 1;  // meaningful on the copy thread only
     float2 dsum = make_float2(0.f, 0.f);  // warp 0: log2 of the decay accumulated over all chunks, channels 2*lane, +1
     for (int ic = 0; ic < nchunks; ++ic) {
         const int c = a.reverse_state ? nchunks - 1 - ic : ic;  // chunk processed in this iteration
@@ -260,7 +263,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         const uint64_t so = (uint64_t)(st * (SM::kStage >> 4));
         WKV6_TSTAMP(ic, 0);
         if (!cta_wait(&bar_full[st], (ic >> 1) & 1, warp)) err = 1;
-        if (tid == 0) --loads_pending;
+        if (copy_thread) --loads_pending;
         WKV6_TSTAMP(ic, 1);
 
         // ---- pass 1: per-step log2 decays of this thread's 8 tokens x 2 channels, running sums from the first of them.
@@ -288,7 +291,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             *reinterpret_cast<float2 *>(&(half ? sTail : sHead)[w4 * 64 + 2 * lane]) = cs;
         }
         // the previous chunk's y tile and checkpoint copies must have left shared memory before it is rewritten
-        if (tid == 0) bulk_wait_read<0>();
+        if (copy_thread) bulk_wait_read<0>();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
         WKV6_TSTAMP(ic, 2);
 
@@ -417,7 +420,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             for (int kk = 0; kk < 4; ++kk)  // A (distances 1..3) = r~ [k~ copies]^T
                 if (!wide) umma_ss(tmAD, dR + so + 2 * kk, dKD + 2 * kk, idKK96, kk > 0);
             umma_commit(bar_mma1);
-        } else if (tid == 32) {
+        } else if (tid == 64) {
             tc_fence_after_sync();
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // state increment = k^^T v   (reverse-state mode: r^^T x2, r^ sits in the w tile)
@@ -491,16 +494,17 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
 
         if (tid == 0) {
             tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // y += A v
+                umma_ss(tmY, dAM + 2 * kk, dV + so + 128 * kk, idKM, true);
+            umma_commit(bar_mma2);
+        } else if (copy_thread) {
             // the state entering the next chunk is complete in shared memory: checkpoint it for the backward.
             // Its read is drained (bulk_wait_read) before the next chunk's first barrier, ahead of the rewrite.
             if (a.ckpt != nullptr && !a.reverse_state && c + 1 < nchunks) {
                 bulk_store(a.ckpt + ((size_t)blockIdx.x * nchunks + c + 1) * 4096, sSB, kTile);
                 bulk_commit();
             }
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // y += A v
-                umma_ss(tmY, dAM + 2 * kk, dV + so + 128 * kk, idKM, true);
-            umma_commit(bar_mma2);
         }
         WKV6_TSTAMP(ic, 7);
         if (!cta_wait(bar_mma2, ic & 1, warp)) err = 3;
@@ -524,7 +528,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         tc_fence_before_sync();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
         WKV6_TSTAMP(ic, 9);
-        if (tid == 0) {
+        if (copy_thread) {
             if (a.write_y) {
                 tma_store_3d(&tm_y, sAM, h * 64, c * kChunk, b);
                 bulk_commit();
@@ -534,7 +538,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     }
 
     // ---- unwind: drain this CTA's copies, report, release tensor memory
-    if (tid == 0) {
+    if (copy_thread) {
         if (err != 0) {
             // loads still in flight target this CTA's shared memory: wait for them (bounded) before leaving
             for (int st = 0; st < 2 && loads_pending > 0; ++st) {
