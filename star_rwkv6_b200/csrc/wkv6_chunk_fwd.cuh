@@ -352,23 +352,44 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 rbv[tt] = *reinterpret_cast<const __nv_bfloat162 *>(pt);
                 kbv[tt] = *reinterpret_cast<const __nv_bfloat162 *>(pt + kTile);
             }
+            // One straight-line block for all eight tokens (no branch inside: the scheduler interleaves the eight
+            // dependency chains exp -> round -> scale -> store); the copies of the rare per-block mode follow separately.
+            __nv_bfloat162 ktv[8], rtv[8];
+            {
+                float2 fe[8], fk2[8];
+#pragma unroll
+                for (int tt = 0; tt < 8; ++tt) {  // exponents, then all exponentials back to back
+                    const float2 xp = (tt == 0) ? make_float2(0.f, 0.f) : x[tt - 1];
+                    fe[tt] = add2(xp, nbase);                                              // c_{t-1} - c_ref
+                    fk2[tt] = make_float2(-nbase.x - x[tt].x, -nbase.y - x[tt].y);         // c_ref - c_t
+                }
+#pragma unroll
+                for (int tt = 0; tt < 8; ++tt) {
+                    fe[tt] = make_float2(ex2f(fe[tt].x), ex2f(fe[tt].y));
+                    fk2[tt] = make_float2(ex2f(fk2[tt].x), ex2f(fk2[tt].y));
+                }
+#pragma unroll
+                for (int tt = 0; tt < 8; ++tt) {
+                    const __nv_bfloat162 rb = rbv[tt], kb = kbv[tt];
+                    const float2 rk = mul2(__bfloat1622float2(rb), __bfloat1622float2(kb));
+                    bon[tt] = fmaf(rk.x, u2.x, rk.y * u2.y);
+                    rtv[tt] = __hmul2(rb, to_bf2(fe[tt]));
+                    ktv[tt] = __hmul2(kb, to_bf2(fk2[tt]));
+                }
+            }
 #pragma unroll
             for (int tt = 0; tt < 8; ++tt) {
                 uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
-                const float2 xp = (tt == 0) ? make_float2(0.f, 0.f) : x[tt - 1];
-                const float2 ea = add2(xp, nbase);                                   // c_{t-1} - c_ref
-                const float2 eb = make_float2(-nbase.x - x[tt].x, -nbase.y - x[tt].y);  // c_ref - c_t
-                const __nv_bfloat162 er = to_bf2(make_float2(ex2f(ea.x), ex2f(ea.y)));
-                const __nv_bfloat162 ek = to_bf2(make_float2(ex2f(eb.x), ex2f(eb.y)));
-                const __nv_bfloat162 rb = rbv[tt], kb = kbv[tt];
-                const float2 rk = mul2(__bfloat1622float2(rb), __bfloat1622float2(kb));
-                bon[tt] = fmaf(rk.x, u2.x, rk.y * u2.y);
-                const __nv_bfloat162 rt = __hmul2(rb, er), kt = __hmul2(kb, ek);
-                *reinterpret_cast<__nv_bfloat162 *>(pt) = rt;                                   // r~
-                *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rt, fR);          // r^ (over w)
-                *reinterpret_cast<__nv_bfloat162 *>(pt + kTile) = kt;                           // k~ distance 0
-                *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(kt, fK);                // k^
-                if (!wide) {
+                *reinterpret_cast<__nv_bfloat162 *>(pt) = rtv[tt];                                  // r~
+                *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rtv[tt], fR);         // r^ (over w)
+                *reinterpret_cast<__nv_bfloat162 *>(pt + kTile) = ktv[tt];                          // k~ distance 0
+                *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(ktv[tt], fK);               // k^
+            }
+            if (!wide) {
+#pragma unroll
+                for (int tt = 0; tt < 8; ++tt) {
+                    uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
+                    const __nv_bfloat162 kt = ktv[tt];
                     if (w4 <= 2) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo) = __hmul2(__hmul2(kt, fD[0]), fE[0]);              // rows [0,48)
                     if (w4 <= 1) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 48 * 128) = __hmul2(__hmul2(kt, fD[1]), fE[1]);   // rows [48,80)
                     if (w4 == 0) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 80 * 128) = __hmul2(__hmul2(kt, fD[2]), fE[2]);   // rows [80,96)
