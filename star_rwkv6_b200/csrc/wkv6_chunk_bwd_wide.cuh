@@ -481,9 +481,9 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         float loc[16];  // G minus its per-channel base (see below)
         {
             const float vga = sVG[ta], vgb = sVG[ta + 8];
-            float gu8[8];
+            float gu8[8], bs8[8];  // per-channel sums over this thread's two tokens: r k vg (for gu) and b (for gw)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) gu8[e] = 0.f;
+            for (int e = 0; e < 8; ++e) gu8[e] = bs8[e] = 0.f;
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 const int col = 8 * (n0 + nn) + 2 * q;
@@ -496,33 +496,36 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                 const float2 fr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&sFRb[col]));
                 const float2 fk = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&sFKb[col]));
                 const float2 uc = *reinterpret_cast<const float2 *>(&sU[col]);
-                float qv[4], bsum0 = 0.f, bsum1 = 0.f;
+                float qv[4];
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
                     const uint32_t off = FO(nn, hrow);
                     const float vg = hrow ? vgb : vga;
-                    const float2 r2 = ld_bf2(sR + off), k2 = ld_bf2(sK + off);
-                    const float2 er = ld_bf2(sET + off), ek = __bfloat1622float2(ekb[2 * nn + hrow]);
-                    // the bf16 operand values r~, k~ exactly as the MMAs saw them
-                    const float2 rt = ld_bf2(sRT + off), kt = ld_bf2(sKT + off);
+                    const __nv_bfloat162 r2b = *reinterpret_cast<const __nv_bfloat162 *>(sR + off);
+                    const __nv_bfloat162 k2b = *reinterpret_cast<const __nv_bfloat162 *>(sK + off);
+                    const __nv_bfloat162 erb = *reinterpret_cast<const __nv_bfloat162 *>(sET + off);
+                    const float2 r2 = __bfloat1622float2(r2b), k2 = __bfloat1622float2(k2b);
+                    const float2 er = __bfloat1622float2(erb), ek = __bfloat1622float2(ekb[2 * nn + hrow]);
+                    // the bf16 operand values r~, k~ exactly as the MMAs saw them (same products, same rounding)
+                    const float2 rt = __bfloat1622float2(__hmul2(r2b, erb)), kt = __bfloat1622float2(__hmul2(k2b, ekb[2 * nn + hrow]));
                     const float2 G1 = make_float2(g1[2 * hrow], g1[2 * hrow + 1]), G2 = make_float2(g2[2 * hrow], g2[2 * hrow + 1]);
                     const float2 H1 = make_float2(h1[2 * hrow], h1[2 * hrow + 1]), H2 = make_float2(h2[2 * hrow], h2[2 * hrow + 1]);
                     const float2 uvg = make_float2(uc.x * vg, uc.y * vg);
                     // gr = Er (GR1 + fR GR2) + u k vg ;  gk = Ek (GK1 + fK GK2) + u r vg
-                    const float2 gr = fma2(er, fma2(fr, G2, G1), mul2(uvg, k2));
+                    const float2 MR = fma2(fr, G2, G1);
+                    const float2 gr = fma2(er, MR, mul2(uvg, k2));
                     const float2 gk = fma2(ek, fma2(fk, H2, H1), mul2(uvg, r2));
                     *reinterpret_cast<__nv_bfloat162 *>(sP + off) = to_bf2(gr);
                     *reinterpret_cast<__nv_bfloat162 *>(sAM + off) = to_bf2(gk);
-                    // gw pieces: a = r~ GR1 + r^ GR2, z = k~ GK1, b = k^ GK2
-                    const float2 av = fma2(rt, G1, mul2(mul2(rt, fr), G2));
-                    const float2 zv = mul2(kt, H1);
+                    // gw pieces: a = r~ GR1 + r^ GR2 = r~ (GR1 + fR GR2) (fR is a power of two), z = k~ GK1, b = k^ GK2
+                    const float2 av = mul2(rt, MR);
                     const float2 bv = mul2(mul2(kt, fk), H2);
-                    const float2 zbv = add2(zv, bv);
+                    const float2 zbv = fma2(kt, H1, bv);
                     qv[2 * hrow] = av.x - zbv.x;
                     qv[2 * hrow + 1] = av.y - zbv.y;
                     loc[4 * nn + 2 * hrow] = -av.x;      // becomes  suffix_incl(q) - q - (z + b) = suffix_incl(q) - a
                     loc[4 * nn + 2 * hrow + 1] = -av.y;
-                    bsum0 += bv.x; bsum1 += bv.y;
+                    bs8[2 * nn] += bv.x; bs8[2 * nn + 1] += bv.y;
                     const float2 rkv = mul2(mul2(r2, k2), make_float2(vg, vg));
                     gu8[2 * nn] += rkv.x;
                     gu8[2 * nn + 1] += rkv.y;
@@ -536,10 +539,26 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                     loc[4 * nn + 2 + e] += pb;
                     if (r0 == 0) sXtot[w4 * 64 + col + e] = pa;
                 }
-                bsum0 += __shfl_xor_sync(0xffffffffu, bsum0, 4); bsum1 += __shfl_xor_sync(0xffffffffu, bsum1, 4);
-                bsum0 += __shfl_xor_sync(0xffffffffu, bsum0, 8); bsum1 += __shfl_xor_sync(0xffffffffu, bsum1, 8);
-                bsum0 += __shfl_xor_sync(0xffffffffu, bsum0, 16); bsum1 += __shfl_xor_sync(0xffffffffu, bsum1, 16);
-                if (r0 == 0) *reinterpret_cast<float2 *>(&sBtot[w4 * 64 + col]) = make_float2(bsum0, bsum1);
+            }
+            {   // block totals of b: 8 channel sums over the 8 lanes that share q, in 7 shuffles; lane r0 ends with channel
+                // value index e = 4*bit4 + 2*bit3 + bit2 of its lane number
+                const bool u4 = (lane & 16) != 0, u3 = (lane & 8) != 0, u2 = (lane & 4) != 0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float send = u4 ? bs8[e] : bs8[e + 4], keep = u4 ? bs8[e + 4] : bs8[e];
+                    bs8[e] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+                }
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float send = u3 ? bs8[e] : bs8[e + 2], keep = u3 ? bs8[e + 2] : bs8[e];
+                    bs8[e] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                }
+                {
+                    const float send = u2 ? bs8[0] : bs8[1], keep = u2 ? bs8[1] : bs8[0];
+                    bs8[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                }
+                const int e = (u4 ? 4 : 0) + (u3 ? 2 : 0) + (u2 ? 1 : 0);  // value index: channel 8 (n0 + e/2) + 2 q + (e & 1)
+                sBtot[w4 * 64 + 8 * (n0 + (e >> 1)) + 2 * q + (e & 1)] = bs8[0];
             }
             {   // running sums of gu live in tensor memory between chunks
                 float acc[8];
