@@ -165,8 +165,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     const int nchunks = (a.T + kChunk - 1) / kChunk;
 
     if (tid == 0) {
-        mbar_init(&bar_full[0], 1);
-        mbar_init(&bar_full[1], 1);
+        mbar_init(&bar_full[0], 4);  // one arrival per loading thread
+        mbar_init(&bar_full[1], 4);
         mbar_init(bar_mma1, 2);  // two issuing threads
         mbar_init(bar_mma2, 1);
         fence_mbar_init();
@@ -220,22 +220,23 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         foB[nn] = sw128_off(ta + 8, 8 * (n0 + nn) + 2 * q);
     }
 
-    auto issue_loads = [&](int ic2) {
+    // Issuing a TMA copy keeps a thread busy for on the order of a hundred cycles, so the copies of one chunk are
+    // spread over warps: lane 0 of warps 2..5 loads one input tile each, lane 0 of warp 1 issues the stores.  Warp 0,
+    // which polls the barriers for the whole CTA and issues MMAs, issues none.
+    const int load_slot = (lane == 0 && warp >= 2 && warp <= 5) ? warp - 2 : -1;  // 0..3 = r, k, v, w
+    auto issue_loads = [&](int ic2) {  // every thread calls it; the four loading threads act
+        if (load_slot < 0) return;
         const int c = a.reverse_state ? nchunks - 1 - ic2 : ic2;
         const int st = ic2 & 1;
-        uint8_t *base = smem + st * SM::kStage;
-        mbar_expect_tx(&bar_full[st], 4 * kTile);
-        tma_load_3d(base, &tm_r, &bar_full[st], h * 64, c * kChunk, b);
-        tma_load_3d(base + kTile, &tm_k, &bar_full[st], h * 64, c * kChunk, b);
-        tma_load_3d(base + 2 * kTile, &tm_v, &bar_full[st], h * 64, c * kChunk, b);
-        tma_load_3d(base + 3 * kTile, &tm_w, &bar_full[st], h * 64, c * kChunk, b);
+        uint8_t *dst = smem + st * SM::kStage + load_slot * kTile;
+        const CUtensorMap *tm = load_slot == 0 ? &tm_r : load_slot == 1 ? &tm_k : load_slot == 2 ? &tm_v : &tm_w;
+        mbar_expect_tx(&bar_full[st], kTile);
+        tma_load_3d(dst, tm, &bar_full[st], h * 64, c * kChunk, b);
     };
-    // Copies (TMA loads and stores, checkpoint stores) are issued by one thread of warp 1, so that warp 0, which
-    // polls the barriers for the whole CTA and issues MMAs, never queues behind them.
     const bool copy_thread = (tid == 32);
+    issue_loads(0);
+    if (nchunks > 1) issue_loads(1);
     if (copy_thread) {
-        issue_loads(0);
-        if (nchunks > 1) issue_loads(1);
         if (a.ckpt != nullptr) {  // state at the start of chunk 0, already in operand layout
             bulk_store(a.ckpt + (size_t)blockIdx.x * nchunks * 4096, sSB, kTile);
             bulk_commit();
@@ -254,7 +255,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     const uint64_t dAM = umma_desc_sw128(smem_u32(sAM)), dSB = umma_desc_sw128(smem_u32(sSB));
 
     int err = 0;
-    int loads_pending = (nchunks > 1) ? 2 : 1;  // meaningful on the copy thread only
+    int loads_issued = (nchunks > 1) ? 2 : 1, loads_consumed = 0;  // chunks whose loads were issued / waited for
     float2 dsum = make_float2(0.f, 0.f);  // warp 0: log2 of the decay accumulated over all chunks, channels 2*lane, +1
     for (int ic = 0; ic < nchunks; ++ic) {
         const int c = a.reverse_state ? nchunks - 1 - ic : ic;  // chunk processed in this iteration
@@ -263,7 +264,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         const uint64_t so = (uint64_t)(st * (SM::kStage >> 4));
         WKV6_TSTAMP(ic, 0);
         if (!cta_wait(&bar_full[st], (ic >> 1) & 1, warp)) err = 1;
-        if (copy_thread) --loads_pending;
+        if (err == 0) ++loads_consumed;
         WKV6_TSTAMP(ic, 1);
 
         // ---- pass 1: per-step log2 decays of this thread's 8 tokens x 2 channels, running sums from the first of them.
@@ -549,25 +550,20 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         tc_fence_before_sync();
         if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
         WKV6_TSTAMP(ic, 9);
-        if (copy_thread) {
-            if (a.write_y) {
-                tma_store_3d(&tm_y, sAM, h * 64, c * kChunk, b);
-                bulk_commit();
-            }
-            if (ic + 2 < nchunks) { issue_loads(ic + 2); ++loads_pending; }
+        if (copy_thread && a.write_y) {
+            tma_store_3d(&tm_y, sAM, h * 64, c * kChunk, b);
+            bulk_commit();
         }
+        if (ic + 2 < nchunks) { issue_loads(ic + 2); ++loads_issued; }
     }
 
     // ---- unwind: drain this CTA's copies, report, release tensor memory
+    if (err != 0 && load_slot >= 0) {
+        // loads still in flight target this CTA's shared memory: wait for them (bounded) before leaving
+        for (int ic2 = loads_consumed; ic2 < loads_issued; ++ic2) mbar_wait(&bar_full[ic2 & 1], (ic2 >> 1) & 1);
+    }
     if (copy_thread) {
-        if (err != 0) {
-            // loads still in flight target this CTA's shared memory: wait for them (bounded) before leaving
-            for (int st = 0; st < 2 && loads_pending > 0; ++st) {
-                for (uint32_t it = 0; it < (1u << 16); ++it)  // parity unknown after an error: poll both
-                    if (mbar_try_wait(&bar_full[st], 0) || mbar_try_wait(&bar_full[st], 1)) break;
-            }
-            atomicExch(&g_chunk_status, err);
-        }
+        if (err != 0) atomicExch(&g_chunk_status, err);
         bulk_wait<0>();
     }
     if (err == 0 && a.dec_out != nullptr && warp == 0)
