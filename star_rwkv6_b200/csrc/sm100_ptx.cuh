@@ -42,13 +42,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     return false;
 }
 
-// Wait of a whole CTA on an mbarrier: warp 0 polls, every other warp sleeps on the CTA barrier instead of
-// spending issue slots on polling.  All threads must call it; the result is uniform.
-__device__ __forceinline__ bool cta_wait(uint64_t *bar, uint32_t parity, int warp) {
-    bool ok = true;
-    if (warp == 0) ok = mbar_wait(bar, parity);
-    return __syncthreads_and(ok) != 0;
-}
+// Wait of every thread of a CTA on an mbarrier.  Each thread observes the phase itself (try_wait suspends the warp
+// in hardware, so this costs next to no issue slots); a CTA barrier behind one polling warp was measured slower.
+// The result may differ between threads when a wait runs out: callers make it uniform at their next CTA barrier.
+__device__ __forceinline__ bool cta_wait(uint64_t *bar, uint32_t parity, int /*warp*/) { return mbar_wait(bar, parity); }
 
 // ---- proxies / fences ------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

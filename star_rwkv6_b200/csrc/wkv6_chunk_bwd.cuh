@@ -261,12 +261,14 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     const uint64_t dAM = umma_desc_sw128(smem_u32(sAM)), dAB = umma_desc_sw128(smem_u32(sAB));
 
     int err = 0;
-    bool load_pending = true;  // thread 0
+    // thread 0: which of the two load barriers still has copies in flight, and the phase parity of their completion
+    bool pend_full = true, pend_late = true;
+    uint32_t pend_parity = 0;
     for (int it = 0; it < nchunks; ++it) {
         const int c = nchunks - 1 - it;
         WKV6_TSTAMP(it, 0);
         if (!cta_wait(bar_full, it & 1, warp)) err = 1;
-        if (tid == 0) load_pending = false;
+        if (tid == 0) pend_full = false;
         WKV6_TSTAMP(it, 1);
 
         // ---- per-step log2 decays and their running sums inside the block (fragment layout)
@@ -419,6 +421,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
             bool ok = true;
             if (warp == 0) ok = mbar_wait(bar_late, it & 1);  // v, gy, S_in have landed (long ago, normally)
             if (!__syncthreads_and(ok && err == 0)) { err = err ? err : 4; break; }
+            if (tid == 0) pend_late = false;
         }
         WKV6_TSTAMP(it, 4);
 
@@ -577,7 +580,11 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
         tc_fence_after_sync();
         WKV6_TSTAMP(it, 9);
         // every input tile is dead once the second MMA group has completed: fetch the next chunk now
-        if (tid == 0 && c > 0 && err == 0) { issue_loads(c - 1); load_pending = true; }
+        if (tid == 0 && c > 0 && err == 0) {
+            issue_loads(c - 1);
+            pend_full = pend_late = true;
+            pend_parity = (uint32_t)(it + 1) & 1u;
+        }
 
         // ---- epilogue 2: gr, gk, gv, gw, one 8-column repetition at a time
         float loc[16];  // G minus its per-channel base (see below)
@@ -691,10 +698,9 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
     // ---- unwind
     if (tid == 0) {
         if (err != 0) {
-            if (load_pending)
-                for (uint32_t k2 = 0; k2 < (1u << 16); ++k2)
-                    if ((mbar_try_wait(bar_full, 0) || mbar_try_wait(bar_full, 1)) &&
-                        (mbar_try_wait(bar_late, 0) || mbar_try_wait(bar_late, 1))) break;
+            // copies still aimed at this CTA's shared memory: wait for them (bounded) before leaving
+            if (pend_full) mbar_wait(bar_full, pend_parity);
+            if (pend_late) mbar_wait(bar_late, pend_parity);
             atomicExch(&g_chunk_status, 100 + err);
         }
         bulk_wait<0>();
