@@ -23,6 +23,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -39,7 +40,7 @@ def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--variant", default="auto", choices=["auto", "seq", "chunk"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
@@ -139,17 +140,54 @@ def run_reference(a):
 # ---- clocks ---------------------------------------------------------------------------------------
 
 class ClockSampler:
+    """SM clock and throttle reasons sampled while the steps run.  Preferred: NVML inside this process, from a thread
+    (a query costs microseconds and leaves the GPU alone).  Fallback: an ``nvidia-smi -lms 200`` child process, whose
+    start-up and queries were measured to slow the timed steps by 4-5 % and occasionally much more."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index):
         self.index = index
-        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.f = None
         self.p = None
+        self.thread = None
+        self.samples = []  # (sm MHz, max MHz, reason bit mask)
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
 
     def start(self):
         try:
+            nv, h = self._nvml_handle()
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            self._stop = threading.Event()
+
+            def loop():
+                while True:
+                    try:
+                        self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), mx,
+                                             nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
+                    except Exception:
+                        pass
+                    if self._stop.wait(0.1):
+                        return
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
+            self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.p = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
                                        "--format=csv,noheader,nounits", "-lms", "200"],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
@@ -158,6 +196,17 @@ class ClockSampler:
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            if self.samples:
+                mask = 0
+                for _, _, m in self.samples:
+                    mask |= int(m)
+                out.update(sm_mhz=float(statistics.median(x[0] for x in self.samples)), sm_max_mhz=float(self.samples[0][1]),
+                           reasons=sorted(n for bit, n in self.REASONS.items() if mask & bit), samples=len(self.samples),
+                           source="nvml")
+            return out
         if self.p is None:
             return out
         self.p.terminate()
