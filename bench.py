@@ -54,6 +54,10 @@ def parse():
                          "0 = automatic: 1 when a rank has at least 256 (batch, head) sequences, else enough to reach 256")
     ap.add_argument("--tshard", action="store_true",
                     help="shard T over the ranks (long sequences): states are carried rank to rank; implies weak=False")
+    ap.add_argument("--workload", default="train", choices=["train", "decode"],
+                    help="train: the headline metric (fwd+bwd).  decode: single-token state updates of an inference step "
+                         "(B16 H64 N64, one fp32 state per layer, --layers of them, replayed from a CUDA graph)")
+    ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-heads", type=int, default=0, help="(b,h) pairs in the CPU sample; 0 = auto")
@@ -399,11 +403,7 @@ def run_b200(a):
                "ms_per_step": e2e_ms, "steps": n_e2e, "api": "RWKVKernelOperator.__call__ + backward, pinned host buffers"}
 
     if rank == 0:
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(peaks_path):
-            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
-        else:
-            peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+        peak, peak_src = measured_peak()
         esz = 2 if a.dtype == "bf16" else 4
         elems = B * T * C
         bwd_bytes, fwd_bytes = 9 * esz * elems, 5 * esz * elems
@@ -439,10 +439,76 @@ def run_b200(a):
         dist.destroy_process_group()
 
 
+def measured_peak():
+    """HBM copy bandwidth measured on this pool (GB/s), or the stated fallback."""
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        return float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def run_decode(a):
+    """One step = one new token for every sequence: the WKV state update of every layer (T = 1).  The fp32 states
+    [layers][B,H,64,64] are read once and written once per step; everything else is a few KB."""
+    import torch
+    import star_rwkv6_b200 as pkg
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    B, H, N, L = (16 if a.B == 8 else a.B), (64 if a.H == 32 else a.H), 64, a.layers
+    C = H * N
+    g = torch.Generator().manual_seed(0)
+    mk = lambda s=1.0: (torch.randn(B, 1, C, generator=g) * s).to(torch.bfloat16).to(dev)
+    ins = [dict(r=mk(0.125), k=mk(0.125), v=mk(0.125), w=(torch.rand(B, 1, C, generator=g) * 7 - 6).to(torch.bfloat16).to(dev))
+           for _ in range(L)]
+    u = (torch.randn(H, N, generator=g) * 0.1).to(dev)
+    states = [(torch.randn(B, H, N, N, generator=g) * 0.1).to(dev) for _ in range(L)]
+
+    def one_step():
+        for d, st in zip(ins, states):
+            pkg.ops.wkv6_decode(d["r"], d["k"], d["v"], d["w"], u, N, state=st, out_state=st)
+
+    for _ in range(3):
+        one_step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(max(3, a.warmup)):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / a.steps
+    state_bytes = 2 * L * B * H * N * N * 4
+    peak, peak_src = measured_peak()
+    achieved = state_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "wkv6_decode_tokens_per_s", "value": B / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps,
+        "warmup": max(3, a.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"wkv6 decode step B{B} H{H} N{N} x {L} layers, bf16 activations, fp32 states",
+                   "l2": f"states of all layers {state_bytes // 2 / 1e6:.0f} MB, larger than the 126 MB L2",
+                   "launch": "one CUDA-graph replay per step"},
+        "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": state_bytes // L, "avg_ms": ms / L},
+        "clocks": clocks, "gpu_launches": L * a.steps,
+    }), flush=True)
+
+
 def main():
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "decode":
+        run_decode(a)
     else:
         run_b200(a)
 
