@@ -54,9 +54,10 @@ def parse():
                          "0 = automatic: 1 when a rank has at least 256 (batch, head) sequences, else enough to reach 256")
     ap.add_argument("--tshard", action="store_true",
                     help="shard T over the ranks (long sequences): states are carried rank to rank; implies weak=False")
-    ap.add_argument("--workload", default="train", choices=["train", "decode"],
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate"],
                     help="train: the headline metric (fwd+bwd).  decode: single-token state updates of an inference step "
-                         "(B16 H64 N64, one fp32 state per layer, --layers of them, replayed from a CUDA graph)")
+                         "(B16 H64 N64, one fp32 state per layer, --layers of them, replayed from a CUDA graph).  gn_gate: the "
+                         "fused per-head GroupNorm + gate after the WKV op, forward + backward, at the B, T, H of config 1")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -503,12 +504,71 @@ def run_decode(a):
     }), flush=True)
 
 
+def run_gn_gate(a):
+    """One step = forward + backward of the fused GroupNorm * gate stage on [B*T, H*N] bf16 tensors."""
+    import torch
+    from star_rwkv6_b200 import group_norm as M
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    rows, H, N = a.B * a.T, a.H, a.N
+    C = H * N
+    g = torch.Generator().manual_seed(0)
+    sets = []
+    for _ in range(2):  # two rotating sets of 3 x 134 MB: larger than L2
+        sets.append(dict(y=(torch.randn(rows, C, generator=g) * 0.03).to(torch.bfloat16).to(dev),
+                         g=torch.nn.functional.silu(torch.randn(rows, C, generator=g)).to(torch.bfloat16).to(dev),
+                         gout=torch.randn(rows, C, generator=g).to(torch.bfloat16).to(dev)))
+    scale = (1 + 0.1 * torch.randn(H, N, generator=g)).to(dev)
+    offset = (0.1 * torch.randn(H, N, generator=g)).to(dev)
+
+    def step(d):
+        out = M.groupnorm_gate_forward_raw(d["y"], d["g"], scale, offset)
+        return out, M.groupnorm_gate_backward_raw(d["y"], d["g"], scale, offset, d["gout"])
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    for i in range(max(3, a.warmup)):
+        step(sets[i % 2])
+    torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(a.steps)]
+    for i in range(a.steps):
+        d = sets[i % 2]
+        ev[i][0].record()
+        out = M.groupnorm_gate_forward_raw(d["y"], d["g"], scale, offset)
+        ev[i][1].record()
+        M.groupnorm_gate_backward_raw(d["y"], d["g"], scale, offset, d["gout"])
+        ev[i][2].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    ms = ev[0][0].elapsed_time(ev[-1][2]) / a.steps
+    elems = rows * C
+    fwd_bytes, bwd_bytes = 6 * elems, 10 * elems
+    peak, peak_src = measured_peak()
+    print(json.dumps({
+        "metric": "gn_gate_fwd_bwd_mtokens_per_s", "value": rows / (ms * 1e-3) / 1e6, "unit": "Mtokens/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": max(3, a.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"per-head GroupNorm * gate, fwd+bwd, rows {rows} H{H} N{N} bf16",
+                   "l2": "two rotating input sets of 403 MB each, larger than the 126 MB L2"},
+        "roofline": {"bound": "hbm", "kernel": "gn_gate_bwd_kernel", "achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "peak": peak,
+                     "unit": "GB/s", "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": bwd_bytes, "avg_ms": bwd_ms,
+                     "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
+                                 "algorithmic_bytes_per_launch": fwd_bytes, "avg_ms": fwd_ms}},
+        "clocks": clocks, "gpu_launches": 3 * a.steps,
+    }), flush=True)
+
+
 def main():
     a = parse()
     if a.impl == "reference":
         run_reference(a)
     elif a.workload == "decode":
         run_decode(a)
+    elif a.workload == "gn_gate":
+        run_gn_gate(a)
     else:
         run_b200(a)
 

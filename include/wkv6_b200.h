@@ -176,6 +176,25 @@ WKV6_API int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const vo
                                   void *stream);
 
 /*
+ * Output stage of the time-mix block, fused: per-head normalisation of the WKV output, then the gate:
+ *   out[row,h,n] = (scale[h,n] * (y[row,h,n] - mean[row,h]) * rstd[row,h] + offset[h,n]) * g[row,h,n],
+ * mean / variance over the N channels of head h of row (= token) `row`, rstd = 1/sqrt(var + eps).  Replaces
+ * GroupNorm.call (rwkv6_model.py:93-99; LayerNormalization(epsilon=64e-5) over the head dimension plus the [H,N]
+ * scale and offset) and the `x * g` that follows it (rwkv6_model.py:158-160).  rows = B*T; y, g, out, gout, gy, gg
+ * are dense [rows, H*N] of one dtype (WKV6_BF16 / WKV6_F16 / WKV6_F32); scale, offset and their gradients are fp32
+ * [H,N].  N == 64, H*N <= 8192, all pointers 16-byte aligned.  The backward needs
+ * wkv6_groupnorm_gate_workspace_bytes(rows, H, N) bytes of scratch (partial sums of the parameter gradients, added in
+ * a fixed order: reruns are bit-identical).
+ */
+WKV6_API int wkv6_groupnorm_gate_forward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y,
+                                         const void *g, const float *scale, const float *offset, void *out, void *stream);
+WKV6_API int wkv6_groupnorm_gate_backward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y,
+                                          const void *g, const float *scale, const float *offset, const void *gout,
+                                          void *gy, void *gg, float *gscale, float *goffset, void *workspace,
+                                          size_t workspace_bytes, void *stream);
+WKV6_API size_t wkv6_groupnorm_gate_workspace_bytes(int64_t rows, int32_t H, int32_t N);
+
+/*
  * XLA legacy custom-call surface.  The library also exports the C++ symbols gpu_ops::rwkv_forward_fn,
  * gpu_ops::rwkv_backward_fn and gpu_ops::rwkv_forward_with_state_fn with the signature
  *     void f(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len)

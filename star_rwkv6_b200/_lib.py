@@ -21,6 +21,7 @@ SYMBOLS = (
     "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
     "wkv6_backward", "wkv6_backward_workspace_bytes", "wkv6_backward_static_scratch", "wkv6_static_scratch_bytes",
     "wkv6_decode", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
+    "wkv6_groupnorm_gate_forward", "wkv6_groupnorm_gate_backward", "wkv6_groupnorm_gate_workspace_bytes",
     "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_descriptor", "wkv6_xla_target",
 )
 
@@ -76,6 +77,13 @@ def _load():
     lib.wkv6_state_scan.argtypes = [i32, i32, i32, i32, vp, vp, vp, vp, vp, ctypes.c_int, vp]
     lib.wkv6_backward_seeded.restype = ctypes.c_int
     lib.wkv6_backward_seeded.argtypes = [pp] + [vp] * 11 + [vp, vp, vp, sz, vp]
+    i64 = ctypes.c_int64
+    lib.wkv6_groupnorm_gate_forward.restype = ctypes.c_int
+    lib.wkv6_groupnorm_gate_forward.argtypes = [i64, i32, i32, i32, ctypes.c_float, vp, vp, vp, vp, vp, vp]
+    lib.wkv6_groupnorm_gate_backward.restype = ctypes.c_int
+    lib.wkv6_groupnorm_gate_backward.argtypes = [i64, i32, i32, i32, ctypes.c_float] + [vp] * 10 + [sz, vp]
+    lib.wkv6_groupnorm_gate_workspace_bytes.restype = sz
+    lib.wkv6_groupnorm_gate_workspace_bytes.argtypes = [i64, i32, i32]
     for name in ("wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state"):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
