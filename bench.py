@@ -123,7 +123,8 @@ def run_reference(a):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    pairs, threads = pick_sample(a, budget_s=3.0)
+    # the sample per step is sized so that warm-up + steps take about two and a half minutes at most
+    pairs, threads = pick_sample(a, budget_s=min(3.0, 150.0 / max(1, a.warmup + a.steps)))
     times, _ = cpu_fwd_bwd(a, pairs, a.warmup + a.steps)
     timed = times[a.warmup:]
     tokens = pairs * a.T / a.H
