@@ -54,10 +54,11 @@ def parse():
                          "0 = automatic: 1 when a rank has at least 256 (batch, head) sequences, else enough to reach 256")
     ap.add_argument("--tshard", action="store_true",
                     help="shard T over the ranks (long sequences): states are carried rank to rank; implies weak=False")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate"],
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate", "shift_mix"],
                     help="train: the headline metric (fwd+bwd).  decode: single-token state updates of an inference step "
                          "(B16 H64 N64, one fp32 state per layer, --layers of them, replayed from a CUDA graph).  gn_gate: the "
-                         "fused per-head GroupNorm + gate after the WKV op, forward + backward, at the B, T, H of config 1")
+                         "fused per-head GroupNorm + gate after the WKV op, forward + backward, at the B, T, H of config 1.  shift_mix: the "
+                         "five token-shift interpolations in front of the projections, forward + backward, same shape")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -562,6 +563,56 @@ def run_gn_gate(a):
     }), flush=True)
 
 
+def run_shift_mix(a):
+    """One step = forward + backward of the five data-dependent token-shift interpolations on [B,T,C] bf16."""
+    import torch
+    from star_rwkv6_b200 import time_mix_inputs as M
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    B, T, C = a.B, a.T, a.H * a.N
+    g = torch.Generator().manual_seed(0)
+    sets = []
+    for _ in range(2):  # two rotating sets (x 134 MB, m and gout 671 MB each): far larger than L2
+        sets.append(dict(x=torch.randn(B, T, C, generator=g).to(torch.bfloat16).to(dev),
+                         m=torch.randn(5, B, T, C, generator=g).to(torch.bfloat16).to(dev),
+                         gout=torch.randn(5, B, T, C, generator=g).to(torch.bfloat16).to(dev)))
+    sampler = ClockSampler(0)
+    sampler.start()
+    for i in range(max(3, a.warmup)):
+        d = sets[i % 2]
+        M._shift_mix_fwd(d["x"], d["m"], False); M._shift_mix_bwd(d["x"], d["m"], d["gout"], False)
+    torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(a.steps)]
+    for i in range(a.steps):
+        d = sets[i % 2]
+        ev[i][0].record()
+        M._shift_mix_fwd(d["x"], d["m"], False)
+        ev[i][1].record()
+        M._shift_mix_bwd(d["x"], d["m"], d["gout"], False)
+        ev[i][2].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    ms = ev[0][0].elapsed_time(ev[-1][2]) / a.steps
+    elems = B * T * C
+    fwd_bytes, bwd_bytes = 22 * elems, 34 * elems  # x + 5 m in, 5 out  |  x + 5 m + 5 gout in, gx + 5 gm out
+    peak, peak_src = measured_peak()
+    print(json.dumps({
+        "metric": "shift_mix5_fwd_bwd_mtokens_per_s", "value": B * T / (ms * 1e-3) / 1e6, "unit": "Mtokens/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": max(3, a.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"five token-shift interpolations, fwd+bwd, B{B} T{T} C{C} bf16",
+                   "l2": "two rotating input sets of 1.5 GB each, larger than the 126 MB L2"},
+        "roofline": {"bound": "hbm", "kernel": "shift_mix_bwd_kernel", "achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "peak": peak,
+                     "unit": "GB/s", "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": bwd_bytes, "avg_ms": bwd_ms,
+                     "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
+                                 "algorithmic_bytes_per_launch": fwd_bytes, "avg_ms": fwd_ms}},
+        "clocks": clocks, "gpu_launches": 2 * a.steps,
+    }), flush=True)
+
+
 def main():
     a = parse()
     if a.impl == "reference":
@@ -570,6 +621,8 @@ def main():
         run_decode(a)
     elif a.workload == "gn_gate":
         run_gn_gate(a)
+    elif a.workload == "shift_mix":
+        run_shift_mix(a)
     else:
         run_b200(a)
 

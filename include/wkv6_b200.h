@@ -195,6 +195,23 @@ WKV6_API int wkv6_groupnorm_gate_backward(int64_t rows, int32_t H, int32_t N, in
 WKV6_API size_t wkv6_groupnorm_gate_workspace_bytes(int64_t rows, int32_t H, int32_t N);
 
 /*
+ * Input stage of the time-mix block: token-shift interpolations
+ *   out_j[b,t,c] = x[b,t,c] + (x[b,t-1,c] - x[b,t,c]) * m_j[b,t,c],   x[b,-1,:] = 0,   j < nmix,
+ * replacing TimeShift (rwkv6_model.py:37-44) plus the multiply-adds of TimeMix.call (rwkv6_model.py:135-146).
+ *   m_is_vector = 1 : nmix = 1, m is one fp32 vector [C] (time_mix_x); out is [B,T,C]
+ *   m_is_vector = 0 : nmix = 1 or 5, m and out are dense [nmix,B,T,C] of the activation dtype (the data-dependent mixes)
+ * x, out, gout, gx are dense [B,T,C] / [nmix,B,T,C] of `dtype`; C a multiple of 8; pointers 16-byte aligned.
+ * Backward: gx [B,T,C], gm = gradient of m ([nmix,B,T,C] of `dtype`, or fp32 [C] for the vector form, which needs
+ * wkv6_shift_mix_workspace_bytes(B,T,C,1) bytes of scratch; its partial sums are added in a fixed order).
+ */
+WKV6_API int wkv6_shift_mix_forward(int32_t B, int32_t T, int32_t C, int32_t dtype, int32_t nmix, int32_t m_is_vector,
+                                    const void *x, const void *m, void *out, void *stream);
+WKV6_API int wkv6_shift_mix_backward(int32_t B, int32_t T, int32_t C, int32_t dtype, int32_t nmix, int32_t m_is_vector,
+                                     const void *x, const void *m, const void *gout, void *gx, void *gm, void *workspace,
+                                     size_t workspace_bytes, void *stream);
+WKV6_API size_t wkv6_shift_mix_workspace_bytes(int32_t B, int32_t T, int32_t C, int32_t m_is_vector);
+
+/*
  * XLA legacy custom-call surface.  The library also exports the C++ symbols gpu_ops::rwkv_forward_fn,
  * gpu_ops::rwkv_backward_fn and gpu_ops::rwkv_forward_with_state_fn with the signature
  *     void f(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len)
