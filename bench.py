@@ -54,11 +54,14 @@ def parse():
                          "0 = automatic: 1 when a rank has at least 256 (batch, head) sequences, else enough to reach 256")
     ap.add_argument("--tshard", action="store_true",
                     help="shard T over the ranks (long sequences): states are carried rank to rank; implies weak=False")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate", "shift_mix"],
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate", "shift_mix", "train_step"],
                     help="train: the headline metric (fwd+bwd).  decode: single-token state updates of an inference step "
                          "(B16 H64 N64, one fp32 state per layer, --layers of them, replayed from a CUDA graph).  gn_gate: the "
                          "fused per-head GroupNorm + gate after the WKV op, forward + backward, at the B, T, H of config 1.  shift_mix: the "
-                         "five token-shift interpolations in front of the projections, forward + backward, same shape")
+                         "five token-shift interpolations in front of the projections, forward + backward, same shape.  train_step: one "
+                         "optimizer step of the 1.6B-shape RWKV-6 model (24 layers, d 2048, ffn 7168, vocab 65536, B8 T4096 per "
+                         "GPU, bf16, AdamW, data parallel with NCCL gradient all-reduce when launched on several GPUs)")
+    ap.add_argument("--no-checkpoint", action="store_true", help="train_step: keep all activations instead of recomputing blocks")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -613,6 +616,90 @@ def run_shift_mix(a):
     }), flush=True)
 
 
+def run_train_step(a):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    from star_rwkv6_b200.model import RWKV6
+    L = 24 if a.layers == 32 else a.layers
+    D, V, FF, B, T = a.H * a.N, 65536, 7168 * (a.H * a.N) // 2048, a.B, a.T
+    torch.manual_seed(0)
+    model = RWKV6(L, V, D, head_size=a.N, decomposer_size=32, expand_size=FF, decay_rank=64).to(dev).to_bf16_()
+    nparams = sum(p.numel() for p in model.parameters())
+    net = model
+    if world > 1:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    g = torch.Generator().manual_seed(1 + rank)
+    host = [torch.randint(0, V, (B, T + 1), generator=g).pin_memory() for _ in range(2)]
+    ckpt = not a.no_checkpoint
+
+    def step(i):
+        tok = host[i % 2].to(dev, non_blocking=True)              # the step's input comes from pinned host memory
+        logits = net(tok[:, :-1], checkpoint_blocks=ckpt)
+        loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, V), tok[:, 1:].reshape(-1))
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    for i in range(max(3, a.warmup)):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.steps):
+        loss = step(i)
+    last = float(loss.detach().cpu())                              # device-to-host read of the step's result
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    if rank == 0:
+        ms = total_ms / a.steps
+        tokens = B * T * world
+        flops = 6.0 * nparams * B * T                                # model FLOPs per GPU and step (recomputation not counted)
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        ach = flops / (ms * 1e-3) / 1e12
+        val = tokens / (ms * 1e-3)
+        print(json.dumps({
+            "metric": "rwkv6_train_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "warmup": max(3, a.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"RWKV-6 training step: {L} layers, d_model {D}, ffn {FF}, vocab {V}, B{B} T{T} per GPU, AdamW",
+                       "parameters": nparams, "block_recomputation": ckpt, "last_loss": last,
+                       "parallelism": f"dp{world}" + (" (DDP, NCCL bucketed all-reduce overlapped with the backward)" if world > 1 else "")},
+            "roofline": {"bound": "tensor", "kernel": "whole step (library GEMMs dominate)", "achieved": ach, "peak": peak,
+                         "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                         "peak_source": "measured (sustained)" if peaks else "fallback"},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": B * (T + 1) * 8, "d2h_bytes_per_step": 4,
+                    "note": "the timed steps already start from pinned host token ids; the loss is read back once at the end"},
+            "clocks": clocks, "gpu_launches": None,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     a = parse()
     if a.impl == "reference":
@@ -623,6 +710,8 @@ def main():
         run_gn_gate(a)
     elif a.workload == "shift_mix":
         run_shift_mix(a)
+    elif a.workload == "train_step":
+        run_train_step(a)
     else:
         run_b200(a)
 
