@@ -13,7 +13,8 @@ import torch
 from torch import nn
 
 from .group_norm import GroupNormGate
-from .ops import wkv6
+from .group_norm import groupnorm_gate_forward_raw
+from .ops import wkv6, wkv6_decode, wkv6_with_state
 from .time_mix_inputs import TimeMixInputs, shift_mix_vector
 
 
@@ -44,6 +45,36 @@ class TimeMix(nn.Module):
         y = wkv6(r, k, v, w, self.time_faaaa, self.head_size)
         return self.dense_o(self.group_norm(y, g))
 
+    def _project(self, xr, xk, xv, xw, xg):
+        r, k, v = self.dense_r(xr), self.dense_k(xk), self.dense_v(xv)
+        w = self.w_b(torch.tanh(self.w_a(xw)))
+        return r, k, v, w, torch.nn.functional.silu(self.dense_g(xg))
+
+    @torch.no_grad()
+    def prefill(self, x):
+        """Forward over a whole prompt; returns the output and the layer state (last input token, WKV state)."""
+        r, k, v, w, g = self._project(*self.mix_inputs(x))
+        y, S = wkv6_with_state(r, k, v, w, self.time_faaaa, self.head_size)
+        gn = self.group_norm
+        return self.dense_o(groupnorm_gate_forward_raw(y, g.contiguous(), gn.scale, gn.offset, gn.epsilon)), (x[:, -1:].clone(), S)
+
+    @torch.no_grad()
+    def decode(self, x, state):
+        """One token ([B,1,D]) with the carried state; the state tensors are updated in place."""
+        x_prev, S = state
+        mi = self.mix_inputs
+        B = x.shape[0]
+        xs = x_prev - x                                                       # TimeShift for a single step
+        x_mix = x + xs * mi.time_mix_x.to(x.dtype)
+        h = torch.tanh(x_mix.reshape(B, -1) @ mi.dense_a.to(x.dtype)).reshape(B, 5, mi.decomposer_size).transpose(0, 1)
+        l = torch.baddbmm(mi.bias_b.to(x.dtype), h, mi.dense_b.to(x.dtype)).reshape(5, B, 1, -1)
+        r, k, v, w, g = self._project(*(x + xs * l))
+        y, _ = wkv6_decode(r, k, v, w, self.time_faaaa, self.head_size, state=S, out_state=S)
+        gn = self.group_norm
+        out = self.dense_o(groupnorm_gate_forward_raw(y, g.contiguous(), gn.scale, gn.offset, gn.epsilon))
+        x_prev.copy_(x)
+        return out
+
 
 class ChannelMix(nn.Module):
     def __init__(self, hidden_size: int, expand_size: int):
@@ -60,6 +91,18 @@ class ChannelMix(nn.Module):
         k = torch.relu(self.dense_key(xk)) ** 2
         return torch.sigmoid(self.dense_receptance(xr)) * self.dense_value(k)
 
+    @torch.no_grad()
+    def prefill(self, x):
+        return self.forward(x), x[:, -1:].clone()
+
+    @torch.no_grad()
+    def decode(self, x, x_prev):
+        xs = x_prev - x
+        k = torch.relu(self.dense_key(x + xs * self.time_mix_k.to(x.dtype))) ** 2
+        out = torch.sigmoid(self.dense_receptance(x + xs * self.time_mix_r.to(x.dtype))) * self.dense_value(k)
+        x_prev.copy_(x)
+        return out
+
 
 class Block(nn.Module):
     def __init__(self, hidden_size, head_size, decomposer_size, expand_size, decay_rank):
@@ -72,6 +115,19 @@ class Block(nn.Module):
     def forward(self, x):
         x = x + self.time_mix(self.layer_norm_att(x))
         return x + self.channel_mix(self.layer_norm_ffn(x))
+
+    @torch.no_grad()
+    def prefill(self, x):
+        o, st_att = self.time_mix.prefill(self.layer_norm_att(x))
+        x = x + o
+        o, st_ffn = self.channel_mix.prefill(self.layer_norm_ffn(x))
+        return x + o, (st_att, st_ffn)
+
+    @torch.no_grad()
+    def decode(self, x, state):
+        st_att, st_ffn = state
+        x = x + self.time_mix.decode(self.layer_norm_att(x), st_att)
+        return x + self.channel_mix.decode(self.layer_norm_ffn(x), st_ffn)
 
 
 class RWKV6(nn.Module):
@@ -97,6 +153,24 @@ class RWKV6(nn.Module):
                 x = checkpoint(blk, x, use_reentrant=False)
             else:
                 x = blk(x)
+        return self.output_layer(self.output_ln(x))
+
+    @torch.no_grad()
+    def prefill(self, tokens):
+        """Prompt pass: logits of the last position [B,1,V] and the per-layer states for ``decode``."""
+        x = self.embedding_ln(self.embedding(tokens))
+        states = []
+        for blk in self.blocks:
+            x, st = blk.prefill(x)
+            states.append(st)
+        return self.output_layer(self.output_ln(x[:, -1:])), states
+
+    @torch.no_grad()
+    def decode(self, token, states):
+        """One new token per sequence ([B,1] ids); ``states`` is updated in place (CUDA-graph friendly)."""
+        x = self.embedding_ln(self.embedding(token))
+        for blk, st in zip(self.blocks, states):
+            x = blk.decode(x, st)
         return self.output_layer(self.output_ln(x))
 
     def to_bf16_(self):

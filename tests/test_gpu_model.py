@@ -86,3 +86,21 @@ def test_model_bf16_step_runs_and_loss_decreases():
         opt.step()
         losses.append(float(loss))
     assert np.isfinite(losses).all() and losses[-1] < losses[0]
+
+
+def test_prefill_then_decode_matches_full_forward():
+    """logits(prompt + n tokens) from one forward pass == prefill(prompt) followed by n single-token decode steps."""
+    from star_rwkv6_b200.model import RWKV6
+    torch.manual_seed(2)
+    V = 300
+    m = RWKV6(num_layers=2, vocabulary_size=V, hidden_size=128, decomposer_size=8, expand_size=256, decay_rank=16).cuda()
+    tok = torch.randint(0, V, (3, 70), device="cuda")
+    with torch.no_grad():
+        full = m(tok)                                   # [B, 70, V]
+        logits, states = m.prefill(tok[:, :64])
+        outs = [logits]
+        for t in range(64, 69):
+            outs.append(m.decode(tok[:, t:t + 1], states))
+    got = torch.cat(outs, 1)                            # positions 63..68
+    want = full[:, 63:69]
+    assert float((got - want).abs().max() / want.abs().max()) <= 1e-4
