@@ -84,7 +84,7 @@ def test_model_bf16_step_runs_and_loss_decreases():
         opt.zero_grad(set_to_none=True)
         loss.backward()
         opt.step()
-        losses.append(float(loss))
+        losses.append(loss.item())
     assert np.isfinite(losses).all() and losses[-1] < losses[0]
 
 
