@@ -1,9 +1,9 @@
 """Generate the golden vectors under tests/golden/ by running the reference's own Python.
 
-Run once, in a container that has the reference checkout (default
-``/root/reference``; override with the REFERENCE_ROOT environment variable):
+Run once, where a checkout of the reference exists (its path in the REFERENCE_ROOT
+environment variable):
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<checkout of infiy-quine/STAR-RWKV6> python tests/golden/make_golden.py
 
 Two reference code paths are executed unmodified:
 
@@ -28,7 +28,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(REPO), "reference")
 sys.path.insert(0, REPO)
 
 from oracle.wkv6_oracle import make_inputs  # noqa: E402
