@@ -5,8 +5,8 @@
 // two CTAs per SM a thread has 128 registers and next to no L1 behind them, so anything the compiler spills is
 // served by L2:
 //   * raw r, k stay in their input tiles (the scaled operands r~, k~ go to tiles of their own), and the factor
-//     e^{c_{t-1}-ref} is parked in a shared-memory tile, so the second epilogue reloads them instead of keeping them
-//     in registers across both MMA groups;
+//     e^{c_{t-1}-ref} is parked in a shared-memory tile, so the second epilogue reloads them (and recomputes r~, k~
+//     as the same bf16 products) instead of keeping them in registers across both MMA groups;
 //   * the fp32 reverse state Abar and the running sum of gu are parked in tensor-memory columns that the per-block
 //     reference points of the general kernel would need for the A copies.
 // A sequence that contains a chunk beyond the limit is abandoned at that chunk: the kernel sets flag[b*H+h] = 1 and
@@ -570,7 +570,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             float gv16[16];
             tmem_ld_16x256b_x4(tmGV + lo + cb, gv16);
 #pragma unroll
-            for (int nn = 0; nn < 4; ++nn) {  // k~ at these positions has been read above, by this thread
+            for (int nn = 0; nn < 4; ++nn) {  // the k~ tile is free: its last reader was the second MMA group
                 *reinterpret_cast<uint32_t *>(sKT + FO(nn, 0)) = pack_bf2(gv16[4 * nn], gv16[4 * nn + 1]);
                 *reinterpret_cast<uint32_t *>(sKT + FO(nn, 1)) = pack_bf2(gv16[4 * nn + 2], gv16[4 * nn + 3]);
             }
@@ -603,7 +603,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                 float2 gw = mul2(mul2(lwf, make_float2(1.0f / kLog2e, 1.0f / kLog2e)),
                                  make_float2(base.x + loc[e0], base.y + loc[e0 + 1]));  // -exp(w) = log-decay
                 if (a.zero_init && c == 0 && ta + 8 * hrow == 0) gw = make_float2(0.f, 0.f);  // no dependence on w_0
-                *reinterpret_cast<__nv_bfloat162 *>(sRT + FO(nn, hrow)) = to_bf2(gw);  // r~ here was read in epilogue 2
+                *reinterpret_cast<__nv_bfloat162 *>(sRT + FO(nn, hrow)) = to_bf2(gw);  // the r~ tile is free: its last reader was the second MMA group
             }
         }
         fence_proxy_async_smem();
