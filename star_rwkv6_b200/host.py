@@ -1,0 +1,99 @@
+"""WKV6 forward + backward for tensors that live in (pinned) host memory.
+
+The reference operator takes device tensors; a caller whose activations sit in host memory pays two PCIe transfers
+per call (5 tensors in, 5 out), which dwarf the kernels.  ``HostPipeline`` streams the batch rows through the GPU in
+slices on a few CUDA streams, so that the host-to-device copy of one slice, the kernels of the previous one and the
+device-to-host copy of the one before run at the same time (the two copy directions use separate DMA engines); a call
+then costs about one direction of PCIe traffic instead of both plus the kernels.  Rows are independent (the recurrence
+never crosses a batch row), so slicing changes no result.  Every slot owns its device buffers, allocated once: the
+calls themselves go straight to the C ABI and allocate nothing.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+from .ops import _ptr, _stream, make_problem, out_dtype
+
+_IN = ("r", "k", "v", "w", "gy")
+_OUT = ("y", "gr", "gk", "gv", "gw")
+
+
+class HostPipeline:
+    def __init__(self, T: int, H: int, head_size: int, dtype=torch.bfloat16, device=None, rows_per_slice: int = 1,
+                 slots: int = 3, variant: int = _lib.VARIANT_AUTO):
+        self.device = torch.device(device if device is not None else "cuda")
+        self.T, self.H, self.N, self.rows, self.variant = T, H, head_size, rows_per_slice, variant
+        C = H * head_size
+        ydt = out_dtype(dtype)
+        self.slots = []
+        with torch.cuda.device(self.device):
+            for _ in range(max(1, slots)):
+                s = {n: torch.empty((rows_per_slice, T, C), dtype=dtype if n != "gy" else ydt, device=self.device) for n in _IN}
+                s.update({n: torch.empty((rows_per_slice, T, C), dtype=ydt, device=self.device) for n in _OUT})
+                s["gu"] = torch.empty((rows_per_slice, H, head_size), dtype=torch.float32, device=self.device)
+                s["stream"] = torch.cuda.Stream(self.device)
+                self.slots.append(s)
+            self.u = torch.empty((H, head_size), dtype=torch.float32, device=self.device)
+            self.gu_sum = torch.zeros((H, head_size), dtype=torch.float32, device=self.device)
+            p = make_problem(self.slots[0]["r"], self.u, head_size, ydt, variant)
+            ck, ws = lib.wkv6_ckpt_bytes(ctypes.byref(p)), lib.wkv6_backward_workspace_bytes(ctypes.byref(p), 1)
+            for s in self.slots:
+                s["ckpt"] = torch.empty((max(ck, 16),), dtype=torch.uint8, device=self.device)
+                s["ws"] = torch.empty((max(ws, 16),), dtype=torch.uint8, device=self.device)
+                s["ws_bytes"] = ws
+
+    def fwd_bwd(self, r, k, v, w, u, gy, out: Optional[Dict[str, torch.Tensor]] = None):
+        """r, k, v, w, gy: [B,T,C] host tensors (pinned, so that the copies overlap); u: [H,N] fp32.  Fills / returns
+        ``out`` (host tensors y, gr, gk, gv, gw) and returns gu [H,N] fp32 on the host.  Synchronises before returning."""
+        B = r.shape[0]
+        host = dict(zip(_IN, (r, k, v, w, gy)))
+        if out is None:
+            out = {n: torch.empty(tuple(r.shape), dtype=self.slots[0][n].dtype).pin_memory() for n in _OUT}
+        main = torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            self.u.copy_(u, non_blocking=True)
+            self.gu_sum.zero_()
+            ready = torch.cuda.Event()
+            ready.record(main)
+            for i, b0 in enumerate(range(0, B, self.rows)):
+                b1 = min(B, b0 + self.rows)
+                n = b1 - b0
+                s = self.slots[i % len(self.slots)]
+                with torch.cuda.stream(s["stream"]):
+                    if i < len(self.slots):
+                        s["stream"].wait_event(ready)
+                    for name in _IN:
+                        s[name][:n].copy_(host[name][b0:b1], non_blocking=True)
+                    d = {name: s[name][:n] for name in _IN + _OUT}
+                    p = make_problem(d["r"], self.u, self.N, d["y"].dtype, self.variant)
+                    st = _stream(self.device)
+                    check(lib.wkv6_forward(ctypes.byref(p), _ptr(d["r"]), _ptr(d["k"]), _ptr(d["v"]), _ptr(d["w"]), _ptr(self.u),
+                                           _ptr(d["y"]), None, None, 0, None, _ptr(s["ckpt"]), st))
+                    check(lib.wkv6_backward(ctypes.byref(p), _ptr(d["r"]), _ptr(d["k"]), _ptr(d["v"]), _ptr(d["w"]), _ptr(self.u),
+                                            _ptr(d["gy"]), _ptr(d["gr"]), _ptr(d["gk"]), _ptr(d["gv"]), _ptr(d["gw"]),
+                                            _ptr(s["gu"]), _ptr(s["ckpt"]), _ptr(s["ws"]), s["ws_bytes"], st))
+                    for name in _OUT:
+                        out[name][b0:b1].copy_(d[name], non_blocking=True)
+                    s["gu_part"] = s["gu"][:n].sum(0)
+                    done = torch.cuda.Event()
+                    done.record(s["stream"])
+                # the running sum of gu is kept on the main stream, in slice order (fixed order: reruns are bit-identical)
+                main.wait_event(done)
+                self.gu_sum += s["gu_part"]
+            for s in self.slots:
+                main.wait_stream(s["stream"])
+            return out, self.gu_sum.to("cpu")
+
+
+def fwd_bwd_host(r, k, v, w, u, gy, head_size: int, out=None, device=None, rows_per_slice: int = 1, slots: int = 3,
+                 variant: int = _lib.VARIANT_AUTO):
+    """One-shot form of ``HostPipeline`` (allocates the device buffers on every call; keep a ``HostPipeline`` for loops)."""
+    B, T, C = r.shape
+    pipe = HostPipeline(T, C // head_size, head_size, dtype=r.dtype, device=device, rows_per_slice=rows_per_slice, slots=slots,
+                        variant=variant)
+    return pipe.fwd_bwd(r, k, v, w, u, gy, out=out)
