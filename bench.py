@@ -96,7 +96,7 @@ def pick_sample(a, budget_s):
     """Number of (b,h) sequences per CPU step: the whole workload if it fits the time budget, else a
     multiple of the thread count that does."""
     from oracle import c_oracle
-    threads = c_oracle.threads()
+    threads = c_oracle.use_all_cores()  # torchrun sets OMP_NUM_THREADS=1 for its workers
     if a.cpu_sample_heads:
         return a.cpu_sample_heads, threads
     probe = max(threads, 8)
@@ -459,7 +459,7 @@ def run_b200(a):
         bwd_bytes, fwd_bytes = 9 * esz * elems, 5 * esz * elems
         # dram__bytes_read.sum + dram__bytes_write.sum per (token, channel) of the chunked backward, from the ncu
         # capture summarised under profiles/ (it scales with the number of (batch, head) sequences)
-        traffic = 18.3 * elems if (vname == "chunk" and a.dtype == "bf16" and not segmented) else None
+        traffic = 17.9 * elems if (vname == "chunk" and a.dtype == "bf16" and not segmented) else None
         achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
         roofline = {
             "bound": "hbm", "kernel": f"{vname} backward", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -470,7 +470,7 @@ def run_b200(a):
             "step": {"achieved": (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9,
                      "frac": (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9 / peak},
         }
-        cpu = None if a.no_cpu_baseline else cpu_baseline(a)
+        cpu = None if (a.no_cpu_baseline or world > 1) else cpu_baseline(a)  # a one-GPU figure
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if a.tshard else a.scaling, "vs_baseline": None,

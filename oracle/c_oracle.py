@@ -30,6 +30,15 @@ def threads() -> int:
     return int(lib().wkv6_oracle_threads_f64())
 
 
+def use_all_cores() -> int:
+    """Run on every core this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its
+    workers).  Returns the thread count now in force."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().wkv6_oracle_set_threads_f64(n)
+    return threads()
+
+
 def _prep(x, dt):
     return np.ascontiguousarray(np.asarray(x, dtype=dt))
 

@@ -34,8 +34,10 @@
 #if defined(_OPENMP)
 #include <omp.h>
 int FN(wkv6_oracle_threads)(void) { return omp_get_max_threads(); }
+void FN(wkv6_oracle_set_threads)(int n) { if (n > 0) omp_set_num_threads(n); }
 #else
 int FN(wkv6_oracle_threads)(void) { return 1; }
+void FN(wkv6_oracle_set_threads)(int n) { (void)n; }
 #endif
 
 static inline REAL decay_of(REAL w) { return (REAL)exp(-exp((double)w)); }
