@@ -417,7 +417,7 @@ def run_b200(a):
             gu_host.copy_(ud.grad, non_blocking=True)
 
         from star_rwkv6_b200.host import HostPipeline
-        pipe = HostPipeline(T, H, N, dtype=xdt, device=dev, rows_per_slice=1, slots=3, variant=variant)
+        pipe = HostPipeline(T, H, N, dtype=xdt, device=dev, rows_per_slice=1, slots=6, variant=variant)
 
         def host_step(hs):  # the package's host-buffer call: batch rows streamed through the GPU, copies overlapped
             pipe.fwd_bwd(hs["r"], hs["k"], hs["v"], hs["w"], u_host, hs["gy"], out=out_host)

@@ -212,6 +212,16 @@ WKV6_API int wkv6_shift_mix_backward(int32_t B, int32_t T, int32_t C, int32_t dt
 WKV6_API size_t wkv6_shift_mix_workspace_bytes(int32_t B, int32_t T, int32_t C, int32_t m_is_vector);
 
 /*
+ * Pitched copy between host and device memory on `stream` (a thin wrapper of cudaMemcpy2DAsync, exported so that a
+ * host-side pipeline bound through this ABI needs no second library): `rows` lines of `width_bytes` bytes, line i at
+ * dst + i*dst_pitch / src + i*src_pitch.  to_host = 0: host to device, 1: device to host.  A head group of a [T, H*N]
+ * activation row in host memory is such a region (pitch H*N elements, width g*N elements).  The reference has no
+ * counterpart: its operators take device tensors only.
+ */
+WKV6_API int wkv6_copy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes,
+                                size_t rows, int32_t to_host, void *stream);
+
+/*
  * XLA legacy custom-call surface.  The library also exports the C++ symbols gpu_ops::rwkv_forward_fn,
  * gpu_ops::rwkv_backward_fn and gpu_ops::rwkv_forward_with_state_fn with the signature
  *     void f(cudaStream_t stream, void **buffers, const char *opaque, size_t opaque_len)

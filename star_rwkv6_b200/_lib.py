@@ -22,7 +22,7 @@ SYMBOLS = (
     "wkv6_backward", "wkv6_backward_workspace_bytes", "wkv6_backward_static_scratch", "wkv6_static_scratch_bytes",
     "wkv6_decode", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
     "wkv6_groupnorm_gate_forward", "wkv6_groupnorm_gate_backward", "wkv6_groupnorm_gate_workspace_bytes",
-    "wkv6_shift_mix_forward", "wkv6_shift_mix_backward", "wkv6_shift_mix_workspace_bytes",
+    "wkv6_shift_mix_forward", "wkv6_shift_mix_backward", "wkv6_shift_mix_workspace_bytes", "wkv6_copy_2d_async",
     "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_descriptor", "wkv6_xla_target",
 )
 
@@ -91,6 +91,8 @@ def _load():
     lib.wkv6_shift_mix_backward.argtypes = [i32] * 6 + [vp] * 6 + [sz, vp]
     lib.wkv6_shift_mix_workspace_bytes.restype = sz
     lib.wkv6_shift_mix_workspace_bytes.argtypes = [i32] * 4
+    lib.wkv6_copy_2d_async.restype = ctypes.c_int
+    lib.wkv6_copy_2d_async.argtypes = [vp, sz, vp, sz, sz, sz, i32, vp]
     for name in ("wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state"):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int

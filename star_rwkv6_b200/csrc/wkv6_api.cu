@@ -78,6 +78,18 @@ const char *wkv6_version(void) { return "wkv6_b200 0.1 (sm_100a)"; }
 
 int wkv6_device_status(void) { return chunk_status(); }
 
+int wkv6_copy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
+                       int32_t to_host, void *stream) {
+    if (width_bytes == 0 || rows == 0) return WKV6_OK;
+    if (dst == nullptr || src == nullptr) return fail(WKV6_ERR_INVALID, "wkv6_copy_2d_async: NULL pointer");
+    if (dst_pitch < width_bytes || src_pitch < width_bytes)
+        return fail(WKV6_ERR_INVALID, "wkv6_copy_2d_async: a pitch is smaller than the line width");
+    cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
+                                      to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice,
+                                      static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "cudaMemcpy2DAsync");
+}
+
 int wkv6_resolve_variant(const wkv6_problem *p) {
     Dims d;
     int rc = validate(p, &d);

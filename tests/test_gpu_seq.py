@@ -145,6 +145,31 @@ def test_state_chaining(pkg):
     assert scaled_err(np_(s), so) <= TOL_F32
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_empty_inputs(pkg, dtype):
+    """No tokens or no sequences: empty outputs, a zero gu, and a final state equal to the (mapped) initial state."""
+    from star_rwkv6_b200 import ops
+    from star_rwkv6_b200.rwkv_kernel.torch_rwkv_kernel import RWKVKernelOperator
+    N, H = 64, 2
+    u = torch.randn(H, N, device="cuda")
+    for B, T in ((2, 0), (0, 5), (0, 0)):
+        z = torch.zeros(B, T, H * N, dtype=dtype, device="cuda")
+        y, s, _ = ops.forward_raw(z, z, z, z, u, N, want_state=True)
+        assert y.shape == (B, T, H * N) and s.shape == (B, H, N, N) and not s.any()
+        gr, gk, gv, gw, gu = ops.backward_raw(z, z, z, z, u, z, N)
+        torch.cuda.synchronize()
+        assert gr.shape == gw.shape == (B, T, H * N) and gu.shape == (B, H, N) and not gu.any()
+    s0 = torch.randn(2, H, N, N, device="cuda")
+    z = torch.zeros(2, 0, H * N, dtype=dtype, device="cuda")
+    y, s = RWKVKernelOperator(N, 16)(z, z, z, z, u, return_state=True, init_state=s0, state_map=[1, 0])
+    assert y.shape == (2, 0, H * N) and torch.equal(s, s0[[1, 0]])
+    t = z.clone().requires_grad_(True)
+    uu = u.clone().requires_grad_(True)
+    y, _ = RWKVKernelOperator(N, 16)(t, t, t, t, uu)
+    y.sum().backward()
+    assert t.grad.shape == t.shape and not uu.grad.any()
+
+
 def test_errors(pkg):
     from star_rwkv6_b200.rwkv_kernel.torch_rwkv_kernel import RWKVKernelOperator
     op = RWKVKernelOperator(64, 16)
