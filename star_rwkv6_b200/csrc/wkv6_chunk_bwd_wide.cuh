@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         tma_load_3d(sK, &tm_k, bar_rk, h * 64, c * kChunk, b);
         pend_rk = true;
     };
-    // Copies are issued by one thread of warp 4, so that warps 0-3, which poll the barriers and issue the MMAs, never
+    // Copies are issued by one thread of warp 4, so that warps 0-3, whose first lanes issue the MMAs, never
     // queue behind them.
     const bool copy_thread = (tid == 128);
     if (copy_thread) { issue_early(nchunks - 1); issue_rk(nchunks - 1); }

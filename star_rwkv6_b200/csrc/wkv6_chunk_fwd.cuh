@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
 
     // Issuing a TMA copy keeps a thread busy for on the order of a hundred cycles, so the copies of one chunk are
     // spread over warps: lane 0 of warps 2..5 loads one input tile each, lane 0 of warp 1 issues the stores.  Warp 0,
-    // which polls the barriers for the whole CTA and issues MMAs, issues none.
+    // whose first lane issues MMAs, issues none.
     const int load_slot = (lane == 0 && warp >= 2 && warp <= 5) ? warp - 2 : -1;  // 0..3 = r, k, v, w
     auto issue_loads = [&](int ic2) {  // every thread calls it; the four loading threads act
         if (load_slot < 0) return;
