@@ -150,6 +150,41 @@ WKV6_API int wkv6_decode(const wkv6_problem *p, const void *r, const void *k, co
                          float *s_out, void *stream);
 
 /*
+ * Decode step with the output stage of the time-mix block fused behind the recurrence:
+ *   out = (GroupNorm_per_head(y) * gn_scale + gn_offset) * silu(g_raw)
+ * (rwkv6_model.py:147 g = silu(dense_g(xg)), :158-160 group_norm then the gate; GroupNorm :84-114 with eps 64e-5).
+ * g_raw is the gate projection before SiLU, [B,1,H*N] of x_dtype; gn_scale / gn_offset are fp32 [H,N].
+ * All other arguments as wkv6_decode.
+ */
+WKV6_API int wkv6_decode_gated(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
+                               const void *u, const void *g_raw, const float *gn_scale, const float *gn_offset, float eps,
+                               void *out, const float *s_in, const int64_t *s_map, int32_t s_kinds, float *s_out,
+                               void *stream);
+
+/*
+ * Element-wise stages of a decode step (T == 1) around the matrix products of an RWKV-6 block, one launch each;
+ * every tensor is dense [B, D] of `dtype` (WKV6_F32 / WKV6_BF16 / WKV6_F16) unless stated.  The reference evaluates
+ * these expressions with framework operations over whole sequences (rwkv6_model.py:37-44,128-146 time shift and
+ * mixes; :48-83 channel mix); at one token per step they are pure launch latency, so they are fused here.
+ *   wkv6_decode_ln_shift_mix: xa = LayerNorm(x; ln_w, ln_b, eps); xs = prev - xa; prev <- xa (in place);
+ *       mix0 = xa + xs * mu0, mix1 = xa + xs * mu1 (mu fp32 [D]; mix1 / mu1, xa_out and xs_out may be NULL). D even, D <= 8192.
+ *   wkv6_decode_lora_mix: h [B, 5R] is x_mix A before tanh (A = the five dense_a kernels side by side);
+ *       out[perm[m]] = xa + xs * (bias[m] + tanh(h[:, mR:(m+1)R]) wb[m]),  wb [5, R, D], bias [5, D], out [5, B, D];
+ *       perm (host pointer to 5 ints, NULL = identity) lets the caller order the outputs for its next products.  D even.
+ *   wkv6_decode_relu_sq: out = max(x, 0)^2 over n elements (channel-mix key activation, rwkv6_model.py:47-48,73).
+ *   wkv6_decode_sigmoid_mul_add: out = x + sigmoid(r) * kv over n elements (channel-mix output plus the residual).
+ */
+WKV6_API int wkv6_decode_ln_shift_mix(int32_t B, int32_t D, int32_t dtype, float eps, const void *x, const void *ln_w,
+                                      const void *ln_b, void *prev, const float *mu0, const float *mu1, void *xa_out,
+                                      void *xs_out, void *mix0, void *mix1, void *stream);
+WKV6_API int wkv6_decode_lora_mix(int32_t B, int32_t D, int32_t R, int32_t dtype, const void *h, const void *wb,
+                                  const void *bias, const void *xa, const void *xs, void *out, const int32_t *perm,
+                                  void *stream);
+WKV6_API int wkv6_decode_relu_sq(int64_t n, int32_t dtype, const void *x, void *out, void *stream);
+WKV6_API int wkv6_decode_sigmoid_mul_add(int64_t n, int32_t dtype, const void *x, const void *r, const void *kv, void *out,
+                                         void *stream);
+
+/*
  * Sequence splitting along T (no counterpart in the reference, whose kernels cap T at a compile-time constant and
  * never split a sequence; BASELINE's long-sequence configuration asks for it).  A sequence cut into G segments is
  * handled as a batch of B*G shorter sequences (a dense [B, G*Tseg, C] tensor is a [B*G, Tseg, C] tensor) whose

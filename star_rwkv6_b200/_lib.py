@@ -20,7 +20,8 @@ VARIANTS = {"auto": VARIANT_AUTO, "seq": VARIANT_SEQ, "chunk": VARIANT_CHUNK}
 SYMBOLS = (
     "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
     "wkv6_backward", "wkv6_backward_workspace_bytes", "wkv6_backward_static_scratch", "wkv6_static_scratch_bytes",
-    "wkv6_decode", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
+    "wkv6_decode", "wkv6_decode_gated", "wkv6_decode_ln_shift_mix", "wkv6_decode_lora_mix", "wkv6_decode_relu_sq",
+    "wkv6_decode_sigmoid_mul_add", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
     "wkv6_groupnorm_gate_forward", "wkv6_groupnorm_gate_backward", "wkv6_groupnorm_gate_workspace_bytes",
     "wkv6_shift_mix_forward", "wkv6_shift_mix_backward", "wkv6_shift_mix_workspace_bytes", "wkv6_copy_2d_async",
     "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_descriptor", "wkv6_xla_target",
@@ -72,6 +73,16 @@ def _load():
     lib.wkv6_static_scratch_bytes.argtypes = []
     lib.wkv6_decode.restype = ctypes.c_int
     lib.wkv6_decode.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, i64p, i32, vp, vp]
+    lib.wkv6_decode_gated.restype = ctypes.c_int
+    lib.wkv6_decode_gated.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_float, vp, vp, i64p, i32, vp, vp]
+    lib.wkv6_decode_ln_shift_mix.restype = ctypes.c_int
+    lib.wkv6_decode_ln_shift_mix.argtypes = [i32, i32, i32, ctypes.c_float] + [vp] * 11
+    lib.wkv6_decode_lora_mix.restype = ctypes.c_int
+    lib.wkv6_decode_lora_mix.argtypes = [i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, ctypes.POINTER(ctypes.c_int32), vp]
+    lib.wkv6_decode_relu_sq.restype = ctypes.c_int
+    lib.wkv6_decode_relu_sq.argtypes = [ctypes.c_int64, i32, vp, vp, vp]
+    lib.wkv6_decode_sigmoid_mul_add.restype = ctypes.c_int
+    lib.wkv6_decode_sigmoid_mul_add.argtypes = [ctypes.c_int64, i32, vp, vp, vp, vp, vp]
     lib.wkv6_segment_summary.restype = ctypes.c_int
     lib.wkv6_segment_summary.argtypes = [pp, vp, vp, vp, ctypes.c_int, vp, vp, vp]
     lib.wkv6_state_scan.restype = ctypes.c_int

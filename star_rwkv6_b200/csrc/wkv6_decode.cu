@@ -10,11 +10,22 @@
 
 namespace wkv6 {
 
+// Optional output stage (GATE): the per-head GroupNorm of the reference's time-mix block and its gate
+// (rwkv6_model.py:158-160 with g = silu(dense_g(xg)), :147), out = (GroupNorm(y) * scale + offset) * silu(g_raw), applied
+// to the 64 outputs of this (batch, head) while they are still in shared memory.
+struct DecodeGate {
+    const void *g_raw;   // [B, H*64] gate projection before SiLU, x_dtype
+    const float *scale;  // [H, 64]
+    const float *offset; // [H, 64]
+    float eps;
+};
+
 // 256 threads per (b, h): thread = (row group ig = tid / 16, column quad jq = tid % 16); rows ig, ig+16, ig+32, ig+48.
+template <bool GATE>
 __global__ void __launch_bounds__(256) decode_kernel(int H, int x_dtype, int y_dtype, int u_dtype, const void *r,
                                                      const void *k, const void *v, const void *w, const void *u,
                                                      const float *s_in, const int64_t *s_map, int s_kinds, float *s_out,
-                                                     void *y) {
+                                                     void *y, DecodeGate gate) {
     __shared__ float sR[64], sK[64], sD[64], sU[64];
     __shared__ __align__(16) float sV[64];
     __shared__ __align__(16) float sY[16][64];
@@ -51,11 +62,32 @@ __global__ void __launch_bounds__(256) decode_kernel(int H, int x_dtype, int y_d
     }
     *reinterpret_cast<float4 *>(&sY[ig][4 * jq]) = acc;
     __syncthreads();
+    float t = 0.f;
     if (tid < 64) {
-        float t = 0.f;
 #pragma unroll
         for (int g = 0; g < 16; ++g) t += sY[g][tid];
-        store_any(y, y_dtype, (size_t)bh * 64 + tid, t);
+    }
+    if (!GATE) {
+        if (tid < 64) store_any(y, y_dtype, (size_t)bh * 64 + tid, t);
+        return;
+    }
+    // GroupNorm over the 64 outputs (two warps), on the values as the ungated kernel would have stored them
+    __shared__ float sRed[4];
+    t = round_to(t, y_dtype);
+    const float s1 = warp_sum(t);
+    if (tid < 64 && (tid & 31) == 0) sRed[tid >> 5] = s1;
+    __syncthreads();
+    const float mean = (sRed[0] + sRed[1]) * (1.f / 64.f);
+    const float c = tid < 64 ? t - mean : 0.f;
+    const float s2 = warp_sum(c * c);
+    if (tid < 64 && (tid & 31) == 0) sRed[2 + (tid >> 5)] = s2;
+    __syncthreads();
+    if (tid < 64) {
+        const float rstd = rsqrtf((sRed[2] + sRed[3]) * (1.f / 64.f) + gate.eps);
+        const size_t o = (size_t)bh * 64 + tid;
+        const float gr = load_any(gate.g_raw, x_dtype, o);
+        const float sg = round_to(gr / (1.f + __expf(-gr)), x_dtype);
+        store_any(y, y_dtype, o, fmaf(c * rstd, gate.scale[h * 64 + tid], gate.offset[h * 64 + tid]) * sg);
     }
 }
 
@@ -63,9 +95,9 @@ __global__ void __launch_bounds__(256) decode_kernel(int H, int x_dtype, int y_d
 
 using namespace wkv6;
 
-extern "C" int wkv6_decode(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
-                           const void *u, void *y, const float *s_in, const int64_t *s_map, int32_t s_kinds,
-                           float *s_out, void *stream) {
+static int decode_launch(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w, const void *u,
+                         void *y, const float *s_in, const int64_t *s_map, int32_t s_kinds, float *s_out,
+                         const DecodeGate *gate, void *stream) {
     Dims d;
     int rc = validate(p, &d);
     if (rc) return rc;
@@ -82,8 +114,29 @@ extern "C" int wkv6_decode(const wkv6_problem *p, const void *r, const void *k, 
         if (reinterpret_cast<uintptr_t>(s_in) % 16) return fail(WKV6_ERR_INVALID, "s_in is not 16-byte aligned");
     }
     if (reinterpret_cast<uintptr_t>(s_out) % 16) return fail(WKV6_ERR_INVALID, "s_out is not 16-byte aligned");
-    decode_kernel<<<p->B * p->H, 256, 0, static_cast<cudaStream_t>(stream)>>>(p->H, p->x_dtype, p->y_dtype, p->u_dtype, r, k, v,
-                                                                            w, u, s_in, s_map, s_kinds, s_out, y);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (gate != nullptr) {
+        if (!gate->g_raw || !gate->scale || !gate->offset) return fail(WKV6_ERR_INVALID, "wkv6_decode_gated: NULL gate argument");
+        decode_kernel<true><<<p->B * p->H, 256, 0, st>>>(p->H, p->x_dtype, p->y_dtype, p->u_dtype, r, k, v, w, u, s_in, s_map,
+                                                         s_kinds, s_out, y, *gate);
+    } else {
+        decode_kernel<false><<<p->B * p->H, 256, 0, st>>>(p->H, p->x_dtype, p->y_dtype, p->u_dtype, r, k, v, w, u, s_in, s_map,
+                                                          s_kinds, s_out, y, DecodeGate{nullptr, nullptr, nullptr, 0.f});
+    }
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "decode_kernel launch");
+}
+
+extern "C" int wkv6_decode(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
+                           const void *u, void *y, const float *s_in, const int64_t *s_map, int32_t s_kinds,
+                           float *s_out, void *stream) {
+    return decode_launch(p, r, k, v, w, u, y, s_in, s_map, s_kinds, s_out, nullptr, stream);
+}
+
+extern "C" int wkv6_decode_gated(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,
+                                 const void *u, const void *g_raw, const float *gn_scale, const float *gn_offset, float eps,
+                                 void *out, const float *s_in, const int64_t *s_map, int32_t s_kinds, float *s_out,
+                                 void *stream) {
+    const DecodeGate gate{g_raw, gn_scale, gn_offset, eps};
+    return decode_launch(p, r, k, v, w, u, out, s_in, s_map, s_kinds, s_out, &gate, stream);
 }

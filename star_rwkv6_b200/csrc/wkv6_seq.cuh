@@ -85,6 +85,13 @@ __device__ __forceinline__ void store_any(void *p, int dtype, size_t i, float x)
     else static_cast<__half *>(p)[i] = __float2half_rn(x);
 }
 
+// x rounded to the storage dtype (what a store followed by a load would give)
+__device__ __forceinline__ float round_to(float x, int dtype) {
+    if (dtype == WKV6_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+    if (dtype == WKV6_F16) return __half2float(__float2half_rn(x));
+    return x;
+}
+
 __device__ __forceinline__ float quad_sum(float x) {
     x += __shfl_xor_sync(0xffffffffu, x, 1);
     x += __shfl_xor_sync(0xffffffffu, x, 2);

@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
+from . import decode_stages as ds
 from .group_norm import GroupNormGate
 from .group_norm import groupnorm_gate_forward_raw
 from .ops import wkv6, wkv6_decode, wkv6_with_state
@@ -76,6 +77,22 @@ class TimeMix(nn.Module):
         return out
 
 
+    @torch.no_grad()
+    def decode_fused(self, x, ln, state):
+        """The block's time-mix half for one token with fused element-wise stages: x [B, D] is the block input (before
+        its LayerNorm ``ln``); returns x + TimeMix(LN(x)).  13 launches: 8 matrix products and 5 kernels of this package."""
+        x_prev, S = state
+        mi, gn, lin = self.mix_inputs, self.group_norm, torch.nn.functional.linear
+        B, D = x.shape
+        x_mix, _, xa, xs = ds.ln_shift_mix(x, ln.weight, ln.bias, ln.eps, x_prev.view(B, D), mi.time_mix_x, want_xa_xs=True)
+        m = ds.lora_mix(x_mix @ mi.dense_a, mi.dense_b, mi.bias_b, xa, xs)            # r, k, v, g, w
+        r, k, v, g_raw = lin(m[0], self.dense_r.weight), lin(m[1], self.dense_k.weight), lin(m[2], self.dense_v.weight), \
+            lin(m[3], self.dense_g.weight)
+        w = torch.addmm(self.w_b.bias, torch.tanh(lin(m[4], self.w_a.weight)), self.w_b.weight.t())
+        z = ds.wkv6_decode_gated(r, k, v, w, self.time_faaaa, g_raw, gn.scale, gn.offset, gn.epsilon, self.head_size, S)
+        return torch.addmm(x, z, self.dense_o.weight.t())
+
+
 class ChannelMix(nn.Module):
     def __init__(self, hidden_size: int, expand_size: int):
         super().__init__()
@@ -104,6 +121,15 @@ class ChannelMix(nn.Module):
         return out
 
 
+    @torch.no_grad()
+    def decode_fused(self, x, ln, x_prev):
+        """x [B, D] is the block's running activation (before ``ln``); returns x + ChannelMix(LN(x)).  6 launches."""
+        lin = torch.nn.functional.linear
+        xk, xr, _, _ = ds.ln_shift_mix(x, ln.weight, ln.bias, ln.eps, x_prev.view(x.shape), self.time_mix_k, self.time_mix_r)
+        kv = lin(ds.relu_sq(lin(xk, self.dense_key.weight)), self.dense_value.weight)
+        return ds.sigmoid_mul_add(x, lin(xr, self.dense_receptance.weight), kv)
+
+
 class Block(nn.Module):
     def __init__(self, hidden_size, head_size, decomposer_size, expand_size, decay_rank):
         super().__init__()
@@ -124,8 +150,12 @@ class Block(nn.Module):
         return x + o, (st_att, st_ffn)
 
     @torch.no_grad()
-    def decode(self, x, state):
+    def decode(self, x, state, fused: bool = True):
         st_att, st_ffn = state
+        if fused:
+            B, _, D = x.shape
+            x2 = self.time_mix.decode_fused(x.reshape(B, D), self.layer_norm_att, st_att)
+            return self.channel_mix.decode_fused(x2, self.layer_norm_ffn, st_ffn).view(B, 1, D)
         x = x + self.time_mix.decode(self.layer_norm_att(x), st_att)
         return x + self.channel_mix.decode(self.layer_norm_ffn(x), st_ffn)
 
@@ -166,11 +196,13 @@ class RWKV6(nn.Module):
         return self.output_layer(self.output_ln(x[:, -1:])), states
 
     @torch.no_grad()
-    def decode(self, token, states):
-        """One new token per sequence ([B,1] ids); ``states`` is updated in place (CUDA-graph friendly)."""
+    def decode(self, token, states, fused: bool = True):
+        """One new token per sequence ([B,1] ids); ``states`` is updated in place (CUDA-graph friendly).  ``fused``:
+        the element-wise stages of every block run as this package's decode-stage kernels (19 launches per block
+        instead of about 40 framework operations); False keeps the plain framework operations."""
         x = self.embedding_ln(self.embedding(token))
         for blk, st in zip(self.blocks, states):
-            x = blk.decode(x, st)
+            x = blk.decode(x, st, fused)
         return self.output_layer(self.output_ln(x))
 
     def to_bf16_(self):
