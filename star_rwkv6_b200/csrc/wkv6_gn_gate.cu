@@ -163,14 +163,26 @@ __global__ void __launch_bounds__(1024) gn_gate_bwd_kernel(int64_t rows, int C, 
     }
 }
 
-// gscale[c] = sum over the CTAs' partial sums, in CTA order (fixed, so reruns are bit-identical)
-__global__ void gn_gate_reduce_kernel(int nparts, int C, const float *__restrict__ partial, float *__restrict__ gscale,
-                                      float *__restrict__ goffset) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= 2 * C) return;
+// gscale[c] = sum over the CTAs' partial sums in a fixed order (reruns are bit-identical): 32 columns x 8 row groups per
+// block, group g adds the partial sums g, g + 8, ... and the eight group sums are added in group order.
+__global__ void __launch_bounds__(256) gn_gate_reduce_kernel(int nparts, int C, const float *__restrict__ partial,
+                                                             float *__restrict__ gscale, float *__restrict__ goffset) {
+    __shared__ float sred[8][33];
+    const int cx = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
     float s = 0.f;
-    for (int pidx = 0; pidx < nparts; ++pidx) s += partial[(size_t)pidx * 2 * C + c];
-    if (c < C) gscale[c] = s; else goffset[c - C] = s;
+    if (c < 2 * C) {
+#pragma unroll 8
+        for (int pidx = grp; pidx < nparts; pidx += 8) s += partial[(size_t)pidx * 2 * C + c];
+    }
+    sred[grp][cx] = s;
+    __syncthreads();
+    if (grp == 0 && c < 2 * C) {
+        float t = sred[0][cx];
+#pragma unroll
+        for (int g2 = 1; g2 < 8; ++g2) t += sred[g2][cx];
+        if (c < C) gscale[c] = t; else goffset[c - C] = t;
+    }
 }
 
 static int gn_grid(int64_t rows) {
@@ -246,7 +258,7 @@ int wkv6_groupnorm_gate_backward(int64_t rows, int32_t H, int32_t N, int32_t dty
         gn_gate_bwd_kernel<float><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, gout, gy, gg, partial);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gn_gate_bwd_kernel launch");
-    gn_gate_reduce_kernel<<<(2 * C + 255) / 256, 256, 0, st>>>(grid, C, partial, gscale, goffset);
+    gn_gate_reduce_kernel<<<(2 * C + 31) / 32, 256, 0, st>>>(grid, C, partial, gscale, goffset);
     e = cudaGetLastError();
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "gn_gate_reduce_kernel launch");
 }

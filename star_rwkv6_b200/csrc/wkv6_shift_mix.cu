@@ -166,13 +166,26 @@ __global__ void __launch_bounds__(256) shift_mix_bwd_kernel(ShiftGeom g, const v
     if (VEC) V8<float>::st(partial, ((size_t)b * g.runs + run) * g.C + oct * 8, gmsum);
 }
 
-// gmu[c] = sum of the per-(batch row, run) partial sums, in a fixed order
-__global__ void shift_mix_reduce_kernel(int nparts, int C, const float *__restrict__ partial, float *__restrict__ gmu) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+// gmu[c] = sum of the per-(batch row, run) partial sums in a fixed order: 32 columns x 8 row groups per block, group g
+// adds the partial sums g, g + 8, ... and the eight group sums are added in group order.
+__global__ void __launch_bounds__(256) shift_mix_reduce_kernel(int nparts, int C, const float *__restrict__ partial,
+                                                               float *__restrict__ gmu) {
+    __shared__ float sred[8][33];
+    const int cx = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
     float s = 0.f;
-    for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * C + c];
-    gmu[c] = s;
+    if (c < C) {
+#pragma unroll 8
+        for (int p = grp; p < nparts; p += 8) s += partial[(size_t)p * C + c];
+    }
+    sred[grp][cx] = s;
+    __syncthreads();
+    if (grp == 0 && c < C) {
+        float t = sred[0][cx];
+#pragma unroll
+        for (int g2 = 1; g2 < 8; ++g2) t += sred[g2][cx];
+        gmu[c] = t;
+    }
 }
 
 static int shift_check(int B, int T, int C, int dtype, int nmix, const char *what) {
@@ -257,7 +270,7 @@ int wkv6_shift_mix_backward(int32_t B, int32_t T, int32_t C, int32_t dtype, int3
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "shift_mix_bwd_kernel launch");
     if (m_is_vector) {
-        shift_mix_reduce_kernel<<<(C + 255) / 256, 256, 0, st>>>(B * g.runs, C, partial, static_cast<float *>(gm));
+        shift_mix_reduce_kernel<<<(C + 31) / 32, 256, 0, st>>>(B * g.runs, C, partial, static_cast<float *>(gm));
         e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "shift_mix_reduce_kernel launch");
     }
