@@ -30,6 +30,21 @@ __global__ void __launch_bounds__(256) decode_kernel(int H, int x_dtype, int y_d
     __shared__ __align__(16) float sV[64];
     __shared__ __align__(16) float sY[16][64];
     const int tid = threadIdx.x, bh = blockIdx.x, b = bh / H, h = bh % H;
+    const int jq = tid & 15, ig = tid >> 4;
+    size_t in_base = 0;
+    if (s_in != nullptr) {
+        int64_t kind = s_map ? s_map[b] : (s_kinds == 1 ? 0 : b);
+        kind = kind < 0 ? 0 : (kind >= s_kinds ? s_kinds - 1 : kind);
+        in_base = ((size_t)kind * H + h) * 4096;
+    }
+    // The state rows are requested first, so that they travel while the operands are staged.  All four are loaded
+    // before the first store: s_in may alias s_out (in-place update), which would
+    // otherwise force every load to wait for the store before it; a thread only ever writes what it has read.
+    float4 st4[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+        st4[m] = s_in ? __ldcs(reinterpret_cast<const float4 *>(s_in + in_base + (size_t)(ig + 16 * m) * 64 + 4 * jq))
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
     if (tid < 64) {
         const size_t o = (size_t)bh * 64 + tid;
         sR[tid] = load_any(r, x_dtype, o);
@@ -39,26 +54,18 @@ __global__ void __launch_bounds__(256) decode_kernel(int H, int x_dtype, int y_d
         sU[tid] = load_any(u, u_dtype, (size_t)h * 64 + tid);
     }
     __syncthreads();
-    const int jq = tid & 15, ig = tid >> 4;
     const float4 v4 = *reinterpret_cast<const float4 *>(&sV[4 * jq]);
-    size_t in_base = 0;
-    if (s_in != nullptr) {
-        int64_t kind = s_map ? s_map[b] : (s_kinds == 1 ? 0 : b);
-        kind = kind < 0 ? 0 : (kind >= s_kinds ? s_kinds - 1 : kind);
-        in_base = ((size_t)kind * H + h) * 4096;
-    }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
         const int i = ig + 16 * m;
-        float4 s = s_in ? __ldg(reinterpret_cast<const float4 *>(s_in + in_base + (size_t)i * 64 + 4 * jq))
-                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 s = st4[m];
         const float ri = sR[i], ki = sK[i], di = sD[i], uk = sU[i] * ki;
         acc.x = fmaf(ri, fmaf(uk, v4.x, s.x), acc.x); s.x = fmaf(di, s.x, ki * v4.x);
         acc.y = fmaf(ri, fmaf(uk, v4.y, s.y), acc.y); s.y = fmaf(di, s.y, ki * v4.y);
         acc.z = fmaf(ri, fmaf(uk, v4.z, s.z), acc.z); s.z = fmaf(di, s.z, ki * v4.z);
         acc.w = fmaf(ri, fmaf(uk, v4.w, s.w), acc.w); s.w = fmaf(di, s.w, ki * v4.w);
-        *reinterpret_cast<float4 *>(s_out + (size_t)bh * 4096 + (size_t)i * 64 + 4 * jq) = s;
+        __stcs(reinterpret_cast<float4 *>(s_out + (size_t)bh * 4096 + (size_t)i * 64 + 4 * jq), s);
     }
     *reinterpret_cast<float4 *>(&sY[ig][4 * jq]) = acc;
     __syncthreads();
