@@ -171,6 +171,7 @@ WKV6_API int wkv6_decode_gated(const wkv6_problem *p, const void *r, const void 
  *   wkv6_decode_lora_mix: h [B, 5R] is x_mix A before tanh (A = the five dense_a kernels side by side);
  *       out[perm[m]] = xa + xs * (bias[m] + tanh(h[:, mR:(m+1)R]) wb[m]),  wb [5, R, D], bias [5, D], out [5, B, D];
  *       perm (host pointer to 5 ints, NULL = identity) lets the caller order the outputs for its next products.  D even.
+ *       Tensor pointers of these two calls must be aligned to two elements (mu to 8 bytes).
  *   wkv6_decode_relu_sq: out = max(x, 0)^2 over n elements (channel-mix key activation, rwkv6_model.py:47-48,73).
  *   wkv6_decode_sigmoid_mul_add: out = x + sigmoid(r) * kv over n elements (channel-mix output plus the residual).
  */

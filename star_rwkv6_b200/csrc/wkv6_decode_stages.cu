@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdint>
+#include <initializer_list>
 #include <type_traits>
 
 #include "wkv6_internal.h"
@@ -178,6 +180,14 @@ __global__ void __launch_bounds__(256) decode_sigmoid_mul_add_kernel(size_t n, i
     }
 }
 
+// the kernels move pairs of elements: every tensor pointer must be aligned to two elements (fp32 vectors to 8 bytes)
+static bool pair_aligned(int dt, std::initializer_list<const void *> ptrs) {
+    const uintptr_t a = 2 * dtype_size(dt);
+    for (const void *p : ptrs)
+        if (p != nullptr && reinterpret_cast<uintptr_t>(p) % a) return false;
+    return true;
+}
+
 static int check_dtype(int dt, const char *what) {
     if (dt != WKV6_BF16 && dt != WKV6_F16 && dt != WKV6_F32) return fail(WKV6_ERR_INVALID, "%s: bad dtype %d", what, dt);
     return WKV6_OK;
@@ -199,6 +209,8 @@ int wkv6_decode_ln_shift_mix(int32_t B, int32_t D, int32_t dtype, float eps, con
     if (B == 0) return WKV6_OK;
     if (!x || !ln_w || !ln_b || !prev || !mu0 || !mix0) return fail(WKV6_ERR_INVALID, "wkv6_decode_ln_shift_mix: NULL argument");
     if (mix1 != nullptr && mu1 == nullptr) return fail(WKV6_ERR_INVALID, "wkv6_decode_ln_shift_mix: mix1 without mu1");
+    if (!pair_aligned(dtype, {x, ln_w, ln_b, prev, xa_out, xs_out, mix0, mix1}) || !pair_aligned(WKV6_F32, {mu0, mu1}))
+        return fail(WKV6_ERR_INVALID, "wkv6_decode_ln_shift_mix: a pointer is not aligned to two elements");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == WKV6_F32)
         decode_ln_shift_mix_kernel<float><<<B, kStageThreads, 0, st>>>(D, x, ln_w, ln_b, eps, prev, mu0, mu1, xa_out, xs_out, mix0, mix1);
@@ -218,6 +230,8 @@ int wkv6_decode_lora_mix(int32_t B, int32_t D, int32_t R, int32_t dtype, const v
         return fail(WKV6_ERR_UNSUPPORTED, "wkv6_decode_lora_mix: B=%d D=%d R=%d (D even, R <= 256)", B, D, R);
     if (B == 0) return WKV6_OK;
     if (!h || !wb || !bias || !xa || !xs || !out) return fail(WKV6_ERR_INVALID, "wkv6_decode_lora_mix: NULL argument");
+    if (!pair_aligned(dtype, {wb, bias, xa, xs, out}))
+        return fail(WKV6_ERR_INVALID, "wkv6_decode_lora_mix: a pointer is not aligned to two elements");
     Perm5 pm;
     bool seen[5] = {false, false, false, false, false};
     for (int m = 0; m < 5; ++m) {

@@ -68,3 +68,28 @@ def test_operator_rejects_cpu_tensors():
     z = torch.zeros(1, 4, 64)
     with pytest.raises(AssertionError):
         op(z, z, z, z, torch.zeros(1, 64))
+
+
+def test_stage_and_copy_argument_checks(L):
+    """Calls that must be refused before anything is launched (fake, never dereferenced addresses)."""
+    lib = L.lib
+    a = 0x1000                                                # an aligned, non-NULL address
+    assert lib.wkv6_decode_ln_shift_mix(2, 7, L.BF16, 1e-5, a, a, a, a, a, None, None, None, a, None, None) == -2   # D odd
+    assert lib.wkv6_decode_ln_shift_mix(2, 16384, L.BF16, 1e-5, a, a, a, a, a, None, None, None, a, None, None) == -2
+    assert lib.wkv6_decode_ln_shift_mix(2, 64, L.BF16, 1e-5, a, a, a, None, a, None, None, None, a, None, None) == -1  # prev NULL
+    assert lib.wkv6_decode_ln_shift_mix(2, 64, L.BF16, 1e-5, a + 2, a, a, a, a, None, None, None, a, None, None) == -1
+    assert b"aligned" in lib.wkv6_last_error()
+    assert lib.wkv6_decode_ln_shift_mix(2, 64, L.BF16, 1e-5, a, a, a, a, a, None, None, None, a, a, None) == -1     # mix1 without mu1
+    assert lib.wkv6_decode_ln_shift_mix(2, 64, 77, 1e-5, a, a, a, a, a, None, None, None, a, None, None) == -1      # dtype
+    assert lib.wkv6_decode_ln_shift_mix(0, 64, L.BF16, 1e-5, None, None, None, None, None, None, None, None, None, None, None) == 0
+    bad = (ctypes.c_int32 * 5)(0, 1, 2, 2, 4)
+    assert lib.wkv6_decode_lora_mix(2, 64, 8, L.BF16, a, a, a, a, a, a, bad, None) == -1
+    assert b"permutation" in lib.wkv6_last_error()
+    assert lib.wkv6_decode_lora_mix(2, 63, 8, L.BF16, a, a, a, a, a, a, None, None) == -2
+    assert lib.wkv6_decode_lora_mix(2, 64, 8, L.F32, a, a + 4, a, a, a, a, None, None) == -1
+    assert lib.wkv6_decode_relu_sq(-1, L.BF16, a, a, None) == -1
+    assert lib.wkv6_decode_relu_sq(0, L.BF16, None, None, None) == 0
+    assert lib.wkv6_decode_sigmoid_mul_add(5, L.BF16, a, None, a, a, None) == -1
+    assert lib.wkv6_copy_2d_async(a, 8, a, 16, 16, 4, 0, None) == -1            # destination pitch below the width
+    assert lib.wkv6_copy_2d_async(None, 16, a, 16, 16, 4, 0, None) == -1
+    assert lib.wkv6_copy_2d_async(None, 0, None, 0, 0, 0, 0, None) == 0          # nothing to copy
