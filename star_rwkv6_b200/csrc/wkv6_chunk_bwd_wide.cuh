@@ -277,18 +277,23 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                 base += sTot[J2 * 64 + i];
                 if (J2 == 1) ref = rintf(base);
             }
-            if (__syncthreads_or(base < kWideLimit2)) { bail = true; break; }
+            // The factors are written whether or not the chunk fits the single reference point; the test itself rides on
+            // the barrier that publishes them (one CTA barrier fewer per chunk), with a second barrier only when it trips.
+            const bool over = base < kWideLimit2;
             sOff[J * 64 + i] = ref - mybase;
             if (J == 0) {
                 sFRb[i] = __float2bfloat16_rn(pow2i(ref));
                 sFKb[i] = __float2bfloat16_rn(ex2f(base - ref));
                 sDtot[i] = ex2f(base);
             }
-        }
-        {
             bool ok = true;
             if (warp == 0) ok = mbar_wait(bar_rk, it & 1);  // r, k have landed (long ago, normally)
-            if (!__syncthreads_and(ok && err == 0)) { err = err ? err : 5; break; }
+            const bool bad = !ok || err != 0;
+            if (__syncthreads_or(over || bad)) {
+                if (__syncthreads_or(bad)) { err = err ? err : 5; break; }
+                bail = true;  // r, k of this chunk have landed and are not read: the unwind's wait returns at once
+                break;
+            }
             if (copy_thread) pend_rk = false;
         }
         WKV6_TSTAMP(it, 3);
