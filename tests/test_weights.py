@@ -110,3 +110,24 @@ def test_imported_model_prefill_decode(golden_dir):
     for t in range(P, tokens.shape[1]):
         out = model.decode(tok[:, t:t + 1], states)
         assert np.abs(out[:, 0].cpu().numpy() - logits[:, t]).max() <= TOL_F32 * scale, t
+
+
+def test_stacked_projection_kernels_follow_parameters(golden_dir):
+    """The [4, D, D] stack behind the batched decode product shares storage with dense_r/k/v/g: an in-place load reaches
+    it, a replaced parameter (dtype change) rebuilds it."""
+    from star_rwkv6_b200.model import RWKV6
+    from star_rwkv6_b200.weights import config_from_pth, load_pth
+    _, sd, _, _ = fixture(golden_dir)
+    model = RWKV6(**config_from_pth(sd))
+    tm = model.blocks[1].time_mix
+    st = tm._stacked_rkvg()
+    D = tm.dense_r.weight.shape[0]
+    assert st.shape == (4, D, D) and tm.dense_k.weight.data_ptr() == st[1].data_ptr()
+    load_pth(model, sd)
+    assert tm._stacked_rkvg() is st
+    assert np.array_equal(st[2].numpy(), sd["blocks.1.att.value.weight"])
+    assert np.array_equal(st[3].numpy(), sd["blocks.1.att.gate.weight"])
+    model.to_bf16_()
+    st2 = tm._stacked_rkvg()
+    assert st2 is not st and st2.dtype == torch.bfloat16 and tm.dense_g.weight.data_ptr() == st2[3].data_ptr()
+    assert torch.equal(st2[0], tm.dense_r.weight.data)
