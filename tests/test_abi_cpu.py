@@ -93,3 +93,23 @@ def test_stage_and_copy_argument_checks(L):
     assert lib.wkv6_copy_2d_async(a, 8, a, 16, 16, 4, 0, None) == -1            # destination pitch below the width
     assert lib.wkv6_copy_2d_async(None, 16, a, 16, 16, 4, 0, None) == -1
     assert lib.wkv6_copy_2d_async(None, 0, None, 0, 0, 0, 0, None) == 0          # nothing to copy
+
+
+def test_missing_library_fails_loudly():
+    """Without the built CUDA library the package does not import: there is no CPU or framework fallback."""
+    import subprocess
+    import sys
+    env = dict(os.environ, WKV6_B200_LIB="/nonexistent/libwkv6_b200.so")
+    r = subprocess.run([sys.executable, "-c", "import star_rwkv6_b200"], cwd=ROOT, env=env, capture_output=True, text=True)
+    assert r.returncode != 0 and "no fallback" in r.stderr
+
+
+def test_product_never_touches_the_oracle():
+    """The oracle is test infrastructure: no file of the package may import or load anything under oracle/."""
+    pkg = os.path.join(ROOT, "star_rwkv6_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f), errors="ignore").read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", text, re.M), f
+                assert "libwkv6_oracle" not in text and "oracle/" not in text, f
