@@ -330,7 +330,7 @@ def run_b200(a):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    for i in range(a.warmup):
+    for i in range(max(3, a.warmup)):  # never fewer than three warm-up steps
         d = devs[i % nsets]
         y, ck = step(d)
         step_bwd(d, ck)
@@ -472,7 +472,7 @@ def run_b200(a):
         }
         cpu = None if (a.no_cpu_baseline or world > 1) else cpu_baseline(a)  # a one-GPU figure
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(3, a.warmup),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if a.tshard else a.scaling, "vs_baseline": None,
             "dtype": "bf16" if a.dtype == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": workload_name(a), "per_gpu": f"B{B} T{T} H{H} N{N}", "variant": vname,
