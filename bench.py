@@ -62,6 +62,8 @@ def parse():
                          "optimizer step of the 1.6B-shape RWKV-6 model (24 layers, d 2048, ffn 7168, vocab 65536, B8 T4096 per "
                          "GPU, bf16, AdamW, data parallel with NCCL gradient all-reduce when launched on several GPUs)")
     ap.add_argument("--no-checkpoint", action="store_true", help="train_step: keep all activations instead of recomputing blocks")
+    ap.add_argument("--framework-loss", action="store_true",
+                    help="train_step: torch's cross_entropy on an fp32 copy of the logits instead of the fused loss kernel")
     ap.add_argument("--decode-steps", type=int, default=256, help="inference: greedy decode steps after the prefill")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-graph", action="store_true",
@@ -672,6 +674,7 @@ def run_train_step(a):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    from star_rwkv6_b200.loss import lm_loss
     from star_rwkv6_b200.model import RWKV6
     L = 24 if a.layers == 32 else a.layers
     D, V, FF, B, T = a.H * a.N, 65536, 7168 * (a.H * a.N) // 2048, a.B, a.T
@@ -689,7 +692,10 @@ def run_train_step(a):
     def step(i):
         tok = host[i % 2].to(dev, non_blocking=True)              # the step's input comes from pinned host memory
         logits = net(tok[:, :-1], checkpoint_blocks=ckpt)
-        loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, V), tok[:, 1:].reshape(-1))
+        if a.framework_loss:
+            loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, V), tok[:, 1:].reshape(-1))
+        else:   # loss and logit gradient in one pass over the bf16 logits (same fp32 softmax arithmetic)
+            loss = lm_loss(logits, tok[:, 1:])
         opt.zero_grad(set_to_none=True)
         loss.backward()
         opt.step()
@@ -733,6 +739,7 @@ def run_train_step(a):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"RWKV-6 training step: {L} layers, d_model {D}, ffn {FF}, vocab {V}, B{B} T{T} per GPU, AdamW",
                        "parameters": nparams, "block_recomputation": ckpt, "last_loss": last,
+                       "loss": "framework cross_entropy on fp32 logits" if a.framework_loss else "fused softmax cross-entropy + logit gradient on bf16 logits",
                        "parallelism": f"dp{world}" + (" (DDP, NCCL bucketed all-reduce overlapped with the backward)" if world > 1 else "")},
             "roofline": {"bound": "tensor", "kernel": "whole step (library GEMMs dominate)", "achieved": ach, "peak": peak,
                          "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,

@@ -186,6 +186,16 @@ WKV6_API int wkv6_decode_sigmoid_mul_add(int64_t n, int32_t dtype, const void *x
                                          void *stream);
 
 /*
+ * Language-model loss in one pass over bf16 logits [rows, V] (fp32 arithmetic): loss[row] = logsumexp(z) - z[target]
+ * and, over the logits themselves, the gradient  z <- (softmax(z) - onehot(target)) * scale  (scale = 1 / rows for a
+ * mean loss).  Rows whose target lies outside [0, V) give zero loss and gradient.  V a multiple of 8, at most 65536;
+ * logits 16-byte aligned.  No counterpart in the reference (its trainer files are empty); used by the training step
+ * around the op, where it replaces about 65 GB of framework traffic per step by 8.6 GB.
+ */
+WKV6_API int wkv6_softmax_xent_bf16(int64_t rows, int32_t V, void *logits_inout, const int64_t *targets, float scale,
+                                    float *loss, void *stream);
+
+/*
  * Sequence splitting along T (no counterpart in the reference, whose kernels cap T at a compile-time constant and
  * never split a sequence; BASELINE's long-sequence configuration asks for it).  A sequence cut into G segments is
  * handled as a batch of B*G shorter sequences (a dense [B, G*Tseg, C] tensor is a [B*G, Tseg, C] tensor) whose
