@@ -54,7 +54,7 @@ def parse():
                          "0 = automatic: 1 when a rank has at least 256 (batch, head) sequences, else enough to reach 256")
     ap.add_argument("--tshard", action="store_true",
                     help="shard T over the ranks (long sequences): states are carried rank to rank; implies weak=False")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate", "shift_mix", "train_step", "inference"],
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate", "shift_mix", "lm_loss", "train_step", "inference"],
                     help="train: the headline metric (fwd+bwd).  decode: single-token state updates of an inference step "
                          "(B16 H64 N64, one fp32 state per layer, --layers of them, replayed from a CUDA graph).  gn_gate: the "
                          "fused per-head GroupNorm + gate after the WKV op, forward + backward, at the B, T, H of config 1.  shift_mix: the "
@@ -663,6 +663,55 @@ def run_shift_mix(a):
     }), flush=True)
 
 
+def run_lm_loss(a):
+    """One step = the fused language-model loss (softmax cross-entropy + logit gradient, one kernel) over 8192 x 65536
+    bf16 logits; two rotating buffers of 1.07 GB each, larger than the 126 MB L2."""
+    import ctypes
+    import torch
+    from star_rwkv6_b200._lib import check, lib
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    rows, V = 8192, 65536
+    g = torch.Generator(device=dev).manual_seed(0)
+    bufs = [(torch.randn(rows, V, generator=g, device=dev) * 3).to(torch.bfloat16) for _ in range(2)]
+    fresh = [b.clone() for b in bufs]
+    targets = torch.randint(0, V, (rows,), generator=g, device=dev)
+    loss = torch.empty(rows, dtype=torch.float32, device=dev)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def step(i):
+        check(lib.wkv6_softmax_xent_bf16(rows, V, bufs[i % 2].data_ptr(), targets.data_ptr(), 1.0 / rows, loss.data_ptr(), st))
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    for i in range(max(3, a.warmup)):
+        step(i)
+    for b, f in zip(bufs, fresh):
+        b.copy_(f)          # real logits again (a step leaves gradients in its buffer)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / a.steps
+    peak, peak_src = measured_peak()
+    nbytes = 2 * rows * V * 2
+    print(json.dumps({
+        "metric": "lm_loss_mtokens_per_s", "value": rows / (ms * 1e-3) / 1e6, "unit": "Mtokens/s", "n_gpus": 1, "steps": a.steps,
+        "warmup": max(3, a.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"softmax cross-entropy + logit gradient, {rows} x {V} bf16 logits",
+                   "l2": "two rotating buffers of 1.07 GB each, larger than the 126 MB L2"},
+        "roofline": {"bound": "hbm", "kernel": "softmax_xent_kernel", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak,
+                     "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": nbytes, "avg_ms": ms},
+        "clocks": clocks, "gpu_launches": a.steps,
+    }), flush=True)
+
+
 def run_train_step(a):
     import torch
     import torch.distributed as dist
@@ -874,6 +923,8 @@ def main():
         run_gn_gate(a)
     elif a.workload == "shift_mix":
         run_shift_mix(a)
+    elif a.workload == "lm_loss":
+        run_lm_loss(a)
     elif a.workload == "train_step":
         run_train_step(a)
     elif a.workload == "inference":
