@@ -72,9 +72,18 @@ WKV6_API const char *wkv6_last_error(void);
 WKV6_API const char *wkv6_version(void);
 
 /* Error word of the device kernels on the current device: 0, or the code of a bounded in-kernel wait that
- * ran out (the kernel then unwinds and leaves its outputs undefined).  Synchronises the device.  The
+ * ran out (the kernel then unwinds - it drains its outstanding copies, frees its tensor memory, returns - and
+ * leaves its outputs undefined).  Every wait is limited to one second of the GPU's global timer.  The call
+ * synchronises the device and clears the word: it reports what happened since the previous query.  The
  * reference has no counterpart: its kernels contain no waits. */
 WKV6_API int wkv6_device_status(void);
+
+/* Host-side failure injection for tests of the error path above; no counterpart in the reference.  On the current
+ * device, wait_limit_ms > 0 sets the time limit of the in-kernel waits (0 restores one second), and
+ * skip_load_chunk >= 0 makes the chunked forward never request the input tiles of that 64-token chunk, so that the
+ * wait for them runs out with nothing in flight (-1 restores normal operation).  The kernel then returns normally
+ * with wkv6_device_status() != 0; nothing faults, traps or hangs.  Synchronises the device. */
+WKV6_API int wkv6_debug_inject(int32_t skip_load_chunk, int64_t wait_limit_ms);
 
 /* Which variant AUTO resolves to for this problem (WKV6_VARIANT_SEQ / _CHUNK), or a negative error. */
 WKV6_API int wkv6_resolve_variant(const wkv6_problem *p);
@@ -197,7 +206,7 @@ WKV6_API int wkv6_softmax_xent_bf16(int64_t rows, int32_t V, void *logits_inout,
 
 /*
  * Sequence splitting along T (no counterpart in the reference, whose kernels cap T at a compile-time constant and
- * never split a sequence; BASELINE's long-sequence configuration asks for it).  A sequence cut into G segments is
+ * never split a sequence; sequences of 131072 tokens need it).  A sequence cut into G segments is
  * handled as a batch of B*G shorter sequences (a dense [B, G*Tseg, C] tensor is a [B*G, Tseg, C] tensor) whose
  * segment g starts from the state the segments before it produce:
  *   1. wkv6_segment_summary: per segment, the state it builds from zero (state_out [B*G,H,N,N] fp32) and the log2

@@ -18,7 +18,7 @@ VARIANTS = {"auto": VARIANT_AUTO, "seq": VARIANT_SEQ, "chunk": VARIANT_CHUNK}
 
 # every symbol include/wkv6_b200.h declares
 SYMBOLS = (
-    "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
+    "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_debug_inject", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
     "wkv6_backward", "wkv6_backward_workspace_bytes", "wkv6_backward_static_scratch", "wkv6_static_scratch_bytes",
     "wkv6_decode", "wkv6_decode_gated", "wkv6_decode_ln_shift_mix", "wkv6_decode_lora_mix", "wkv6_decode_relu_sq",
     "wkv6_decode_sigmoid_mul_add", "wkv6_softmax_xent_bf16", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
@@ -57,6 +57,8 @@ def _load():
     lib.wkv6_version.argtypes = []
     lib.wkv6_device_status.restype = ctypes.c_int
     lib.wkv6_device_status.argtypes = []
+    lib.wkv6_debug_inject.restype = ctypes.c_int
+    lib.wkv6_debug_inject.argtypes = [ctypes.c_int32, ctypes.c_int64]
     lib.wkv6_resolve_variant.restype = ctypes.c_int
     lib.wkv6_resolve_variant.argtypes = [pp]
     lib.wkv6_forward.restype = ctypes.c_int

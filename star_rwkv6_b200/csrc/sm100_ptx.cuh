@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a features the chunked kernels use: mbarrier,
 // TMA (cp.async.bulk.tensor), tcgen05 (TMEM allocation, UMMA issue/commit, TMEM loads) and
-// the shared-memory / instruction descriptors of tcgen05.mma.  Every wait is bounded: a
+// the shared-memory / instruction descriptors of tcgen05.mma.  Every wait is bounded by a time limit: a
 // wait that runs out returns false and the caller records an error and unwinds.
 #pragma once
 
@@ -34,12 +34,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: ~2^22 polls (each try_wait itself blocks for a hardware-defined slice), far beyond any
-// legitimate latency of one chunk; returns false when it gives up.
+// Limit of every in-kernel wait, in nanoseconds of the GPU's global timer (one second unless the host changes it:
+// wkv6_debug_inject).  A wait that lasts longer gives up: the kernel records an error code and unwinds.
+__device__ unsigned long long g_wait_limit_ns = 1000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: polls (each try_wait itself suspends the warp for a hardware-defined slice) until the phase
+// completes or the time limit has passed; returns false when it gives up.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t it = 0; it < (1u << 22); ++it)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    const unsigned long long limit = *reinterpret_cast<volatile unsigned long long *>(&g_wait_limit_ns);
+    for (;;) {
+#pragma unroll 1
+        for (int it = 0; it < 32; ++it)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > limit) return false;
+    }
 }
 
 // Wait of every thread of a CTA on an mbarrier.  Each thread observes the phase itself (try_wait suspends the warp

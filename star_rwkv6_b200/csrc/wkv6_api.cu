@@ -78,6 +78,8 @@ const char *wkv6_version(void) { return "wkv6_b200 0.1 (sm_100a)"; }
 
 int wkv6_device_status(void) { return chunk_status(); }
 
+int wkv6_debug_inject(int32_t skip_load_chunk, int64_t wait_limit_ms) { return chunk_debug_inject(skip_load_chunk, wait_limit_ms); }
+
 int wkv6_copy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
                        int32_t to_host, void *stream) {
     if (width_bytes == 0 || rows == 0) return WKV6_OK;

@@ -190,10 +190,23 @@ int chunk_state_scan(int B, int H, int G, const float *dec, const float *bsum, c
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "state_scan_kernel launch");
 }
 
+// Read and clear: the word reports what happened since the previous query.  (cudaMemcpyFromSymbol synchronises.)
 int chunk_status() {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_chunk_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_chunk_status, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
     return v;
+}
+
+// Test hook behind wkv6_debug_inject: the time limit of the in-kernel waits and the chunk whose loads the forward skips.
+int chunk_debug_inject(int skip_load_chunk, long long wait_limit_ms) {
+    const unsigned long long ns = wait_limit_ms > 0 ? (unsigned long long)wait_limit_ms * 1000000ull : 1000000000ull;
+    cudaError_t e = cudaMemcpyToSymbol(ptx::g_wait_limit_ns, &ns, sizeof(ns));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_skip_load_chunk, &skip_load_chunk, sizeof(int));
+    return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "cudaMemcpyToSymbol(debug hooks)");
 }
 
 }  // namespace wkv6

@@ -38,17 +38,17 @@ constexpr float kMinLogDecay2 = -10.0f * 1.4426950408889634f;  // clamp of the p
 // for the block distances 1..3 are not needed.
 constexpr float kWideLimit2 = -96.0f;
 
-// device-side error word: 0 = fine, otherwise the code of the wait that ran out
+// device-side error word: 0 = fine, otherwise the code of the wait that ran out (read and cleared by the host)
 __device__ int g_chunk_status;
+// Test hook (wkv6_debug_inject): the forward never requests the input tiles of this chunk index (-1 = off), so the
+// wait for them runs out with no copy outstanding and the kernel takes its error path.
+__device__ int g_skip_load_chunk = -1;
 
 // Phase timestamps of CTA 0 (builds with -DWKV6_TIMING only): g_chunk_timing[chunk][phase] = clock64()
 #ifdef WKV6_TIMING
 __device__ long long g_chunk_timing[64][16];
 #define WKV6_TSTAMP(iter, k) \
     do { if (blockIdx.x == 0 && threadIdx.x == 0 && (iter) < 64) g_chunk_timing[(iter)][(k)] = clock64(); } while (0)
-#elif defined(WKV6_MARK)
-// phase markers in the generated PTX (for counting instructions per phase)
-#define WKV6_TSTAMP(iter, k) asm volatile("// WKV6_MARK " #k ::: "memory")
 #else
 #define WKV6_TSTAMP(iter, k) do { } while (0)
 #endif
@@ -224,8 +224,9 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     // spread over warps: lane 0 of warps 2..5 loads one input tile each, lane 0 of warp 1 issues the stores.  Warp 0,
     // whose first lane issues MMAs, issues none.
     const int load_slot = (lane == 0 && warp >= 2 && warp <= 5) ? warp - 2 : -1;  // 0..3 = r, k, v, w
+    const int skip_chunk = *reinterpret_cast<volatile int *>(&g_skip_load_chunk);  // test hook, -1 in normal use
     auto issue_loads = [&](int ic2) {  // every thread calls it; the four loading threads act
-        if (load_slot < 0) return;
+        if (load_slot < 0 || ic2 == skip_chunk) return;
         const int c = a.reverse_state ? nchunks - 1 - ic2 : ic2;
         const int st = ic2 & 1;
         uint8_t *dst = smem + st * SM::kStage + load_slot * kTile;
@@ -560,7 +561,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     // ---- unwind: drain this CTA's copies, report, release tensor memory
     if (err != 0 && load_slot >= 0) {
         // loads still in flight target this CTA's shared memory: wait for them (bounded) before leaving
-        for (int ic2 = loads_consumed; ic2 < loads_issued; ++ic2) mbar_wait(&bar_full[ic2 & 1], (ic2 >> 1) & 1);
+        for (int ic2 = loads_consumed; ic2 < loads_issued; ++ic2)
+            if (ic2 != skip_chunk) mbar_wait(&bar_full[ic2 & 1], (ic2 >> 1) & 1);
     }
     if (copy_thread) {
         if (err != 0) atomicExch(&g_chunk_status, err);

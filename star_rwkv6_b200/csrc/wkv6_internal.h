@@ -33,6 +33,7 @@ int seq_backward(const wkv6_problem *p, const Dims &d, const void *r, const void
 // chunked tensor-core variant (wkv6_chunk.cu)
 bool chunk_supported(const wkv6_problem *p);
 int chunk_status();
+int chunk_debug_inject(int skip_load_chunk, long long wait_limit_ms);
 size_t chunk_ckpt_bytes(const wkv6_problem *p);
 size_t chunk_backward_workspace(const wkv6_problem *p, const Dims &d, int have_ckpt);
 int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v, const void *w,

@@ -63,16 +63,18 @@ int wkv6_backward_static_scratch(const wkv6_problem *p, const void *r, const voi
         if (ptr == nullptr || reinterpret_cast<uintptr_t>(ptr) % 16) return fail(WKV6_ERR_INVALID, "an input pointer is NULL or not 16-byte aligned");
     for (void *ptr : outs)
         if (ptr == nullptr || reinterpret_cast<uintptr_t>(ptr) % 16) return fail(WKV6_ERR_INVALID, "an output pointer is NULL or not 16-byte aligned");
-    const size_t need = (size_t)q.B * q.T * d.C * sizeof(float);
+    const size_t need = seq_backward_workspace(&q, d);  // 0 for dense fp32 problems: they stage inside gw
     if (need > kStaticScratchBytes)
         return fail(WKV6_ERR_WORKSPACE,
                     "B*T*H*N = %zu (token, channel) pairs need %zu bytes of scratch; the built-in scratch holds %zu bytes "
                     "(%zu pairs) - use wkv6_backward with a caller workspace for larger problems",
                     need / sizeof(float), need, kStaticScratchBytes, kStaticScratchBytes / sizeof(float));
     void *scratch = nullptr;
-    rc = static_scratch_address(&scratch);
-    if (rc) return rc;
+    if (need > 0) {
+        rc = static_scratch_address(&scratch);
+        if (rc) return rc;
+    }
     // Nothing in the scratch has to start at zero: the ascending sweep writes every element the descending sweep reads.
     // (Dense fp32 problems stage that data inside the gw output instead and leave the array untouched.)
-    return seq_backward(&q, d, r, k, v, w, u, gy, gr, gk, gv, gw, gu, scratch, kStaticScratchBytes, st);
+    return seq_backward(&q, d, r, k, v, w, u, gy, gr, gk, gv, gw, gu, scratch, need > 0 ? kStaticScratchBytes : 0, st);
 }

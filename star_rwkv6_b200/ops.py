@@ -184,7 +184,11 @@ def _forward_op(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tens
 @_forward_op.register_fake
 def _(r, k, v, w, u, head_size, want_ckpt, variant):
     y = torch.empty(r.shape, dtype=out_dtype(r.dtype), device=r.device)
-    return y, torch.empty((0,), dtype=torch.uint8, device=r.device)
+    B, T, C = r.shape
+    nbytes = 0
+    if want_ckpt and head_size == 64 and r.dtype == torch.bfloat16 and variant != _lib.VARIANT_SEQ and T >= 1:
+        nbytes = B * (C // head_size) * ((T + 63) // 64) * 4096 * 2   # wkv6_ckpt_bytes of the chunked variant
+    return y, torch.empty((nbytes,), dtype=torch.uint8, device=r.device)
 
 
 @torch.library.custom_op("wkv6_b200::backward", mutates_args=(), device_types="cuda")

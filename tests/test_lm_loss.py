@@ -55,3 +55,8 @@ def test_lm_loss_falls_back_for_other_shapes():
     targets = torch.tensor([0, 5, 12, 3], device="cuda")
     want = torch.nn.functional.cross_entropy(logits.float(), targets)
     assert abs(lm_loss(logits, targets).item() - want.item()) <= 1e-6
+    # masked targets: the same definition as the fused path (zero loss for the row, mean over all rows)
+    masked = torch.tensor([0, -100, 12, 40], device="cuda")
+    rows = torch.nn.functional.cross_entropy(logits.float(), masked.clamp(0, 12), reduction="none")
+    want = (rows[0] + rows[2]) / 4
+    assert abs(lm_loss(logits, masked).item() - want.item()) <= 1e-6

@@ -22,7 +22,7 @@ def _call_static(L, ops, t, u, N, ydt):
     r = t["r"]
     B, T, C = r.shape
     p = ops.make_problem(r, u, N, ydt, L.VARIANT_AUTO)  # the entry point ignores the variant field
-    outs = [torch.empty_like(r, dtype=ydt) for _ in range(4)]
+    outs = [ops._out_like(r, ydt) for _ in range(4)]   # same strides as the inputs (a head-sharded view stays a view)
     gu = torch.empty((B, C // N, N), dtype=torch.float32, device=r.device)
     ptr = lambda x: ctypes.c_void_p(x.data_ptr())
     rc = L.lib.wkv6_backward_static_scratch(ctypes.byref(p), ptr(t["r"]), ptr(t["k"]), ptr(t["v"]), ptr(t["w"]), ptr(u),
@@ -49,6 +49,26 @@ def test_matches_workspace_entry_point_twice(dtype, tol):
             assert np.isfinite(np_(a)).all(), (call, name)
             assert scaled_err(np_(a), np_(b)) <= tol, (call, name)
             assert torch.equal(a, b), (call, name)  # same kernels, same order of operations
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, TOL_BF16), (torch.float32, TOL_F32)])
+def test_head_sharded_view_uses_the_array(dtype, tol):
+    """A column range of a wider tensor (row stride > H*N): also in fp32 this path keeps its scratch in the array."""
+    import star_rwkv6_b200 as pkg
+    from star_rwkv6_b200 import _lib as L, ops
+    N, B, T, H = 64, 2, 130, 4
+    for call, seed in enumerate((61, 62)):
+        d = O.make_inputs(B, T, H, N, seed=seed)
+        wide = {n: torch.tensor(d[n]).to(dtype).cuda() for n in ("r", "k", "v", "w", "gy")}
+        t = {n: x[:, :, N:3 * N] for n, x in wide.items()}           # heads 1..2 of 4, no copy
+        u = torch.tensor(d["u"]).cuda()[1:3].contiguous()
+        ydt = ops.out_dtype(dtype)
+        want = pkg.backward_raw(t["r"], t["k"], t["v"], t["w"], u, t["gy"], N, variant=pkg.VARIANT_SEQ)
+        got = _call_static(L, ops, t, u, N, ydt)
+        torch.cuda.synchronize()
+        for name, a, b in zip(("gr", "gk", "gv", "gw", "gu"), got, want):
+            assert scaled_err(np_(a), np_(b)) <= tol, (call, name)
+            assert torch.equal(a, b), (call, name)
 
 
 def test_rejects_sizes_beyond_the_built_in_scratch():
