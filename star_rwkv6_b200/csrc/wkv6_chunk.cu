@@ -213,6 +213,6 @@ int chunk_debug_inject(int skip_load_chunk, long long wait_limit_ms) {
 
 #ifdef WKV6_TIMING
 extern "C" __attribute__((visibility("default"))) int wkv6_debug_timing(long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, wkv6::g_chunk_timing, sizeof(long long) * 64 * 16);
+    return (int)cudaMemcpyFromSymbol(out, wkv6::g_chunk_timing, sizeof(long long) * 64 * 16 * 8);
 }
 #endif

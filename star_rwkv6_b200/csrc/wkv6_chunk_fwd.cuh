@@ -44,14 +44,23 @@ __device__ int g_chunk_status;
 // wait for them runs out with no copy outstanding and the kernel takes its error path.
 __device__ int g_skip_load_chunk = -1;
 
-// Phase timestamps of CTA 0 (builds with -DWKV6_TIMING only): g_chunk_timing[chunk][phase] = clock64()
+// Phase timestamps of CTA 0 (builds with -DWKV6_TIMING only): g_chunk_timing[chunk][phase][warp] = clock64() of lane 0
 #ifdef WKV6_TIMING
-__device__ long long g_chunk_timing[64][16];
+__device__ long long g_chunk_timing[64][16][8];
 #define WKV6_TSTAMP(iter, k) \
-    do { if (blockIdx.x == 0 && threadIdx.x == 0 && (iter) < 64) g_chunk_timing[(iter)][(k)] = clock64(); } while (0)
+    do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (iter) < 64) g_chunk_timing[(iter)][(k)][threadIdx.x >> 5] = clock64(); } while (0)
 #else
 #define WKV6_TSTAMP(iter, k) do { } while (0)
 #endif
+
+#ifndef WKV6_KO
+#define WKV6_KO 0
+#endif
+#define KO(n) (((WKV6_KO) >> (n)) & 1)
+#ifndef WKV6_EXP
+#define WKV6_EXP 0
+#endif
+#define EXP(n) (((WKV6_EXP) >> (n)) & 1)
 
 struct ChunkFwdSmem {
     static constexpr int kStage = 4 * kTile;                 // r, k, v, w
@@ -283,10 +292,10 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 const uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
                 const float2 w2 = ld_bf2(pt + 3 * kTile);
                 const float2 e2 = mul2(w2, make_float2(kLog2e, kLog2e));
-                float2 l2 = mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
+                float2 l2 = KO(3) ? make_float2(-0.5f, -0.5f) : mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
                 l2.x = fmaxf(l2.x, kMinLogDecay2);
                 l2.y = fmaxf(l2.y, kMinLogDecay2);
-                if (!full_chunk && c * kChunk + 16 * w4 + 8 * half + tt >= a.T) l2 = make_float2(0.f, 0.f);
+                if (!KO(3) && !full_chunk && c * kChunk + 16 * w4 + 8 * half + tt >= a.T) l2 = make_float2(0.f, 0.f);
                 cs = add2(cs, l2);
                 x[tt] = cs;
             }
@@ -348,6 +357,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             const int kdo = (int)(sKD - sR), kho = (int)(sKH - sR);  // uniform offsets of the copy tiles from this stage
             // all loads first: shared-memory loads cannot be scheduled across the stores below
             __nv_bfloat162 rbv[8], kbv[8];
+            if (!KO(8)) {
 #pragma unroll
             for (int tt = 0; tt < 8; ++tt) {
                 const uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
@@ -367,14 +377,16 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 }
 #pragma unroll
                 for (int tt = 0; tt < 8; ++tt) {
+                    if (!KO(4)) {
                     fe[tt] = make_float2(ex2f(fe[tt].x), ex2f(fe[tt].y));
                     fk2[tt] = make_float2(ex2f(fk2[tt].x), ex2f(fk2[tt].y));
+                    }
                 }
 #pragma unroll
                 for (int tt = 0; tt < 8; ++tt) {
                     const __nv_bfloat162 rb = rbv[tt], kb = kbv[tt];
                     const float2 rk = mul2(__bfloat1622float2(rb), __bfloat1622float2(kb));
-                    bon[tt] = fmaf(rk.x, u2.x, rk.y * u2.y);
+                    bon[tt] = KO(0) ? 0.f : fmaf(rk.x, u2.x, rk.y * u2.y);
                     rtv[tt] = __hmul2(rb, to_bf2(fe[tt]));
                     ktv[tt] = __hmul2(kb, to_bf2(fk2[tt]));
                 }
@@ -383,9 +395,9 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             for (int tt = 0; tt < 8; ++tt) {
                 uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
                 *reinterpret_cast<__nv_bfloat162 *>(pt) = rtv[tt];                                  // r~
-                *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rtv[tt], fR);         // r^ (over w)
+                if (!KO(2)) *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rtv[tt], fR);         // r^ (over w)
                 *reinterpret_cast<__nv_bfloat162 *>(pt + kTile) = ktv[tt];                          // k~ distance 0
-                *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(ktv[tt], fK);               // k^
+                if (!KO(2)) *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(ktv[tt], fK);               // k^
             }
             if (!wide) {
 #pragma unroll
@@ -397,6 +409,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                     if (w4 == 0) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 80 * 128) = __hmul2(__hmul2(kt, fD[2]), fE[2]);   // rows [80,96)
                 }
             }
+            }
+            if (!KO(0) && !KO(8)) {
             // sum the bonus partials over the 32 channel pairs: 8 values across 32 lanes in 9 shuffles
             {
                 const bool up = (lane & 16) != 0;
@@ -427,6 +441,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             if ((lane & 3) == 0) {
                 const int tok = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
                 sBonus[16 * w4 + 8 * half + tok] = bon[0];
+            }
             }
         }
         fence_proxy_async_smem();
@@ -462,7 +477,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         // This warp covers column blocks J = 2*half and 2*half + 1 of row block I = w4.
         const float bonus_a = sBonus[ta], bonus_b = sBonus[ta + 8];
         const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
-        {
+        if (!KO(5)) {
             const int I = w4;
 #pragma unroll
             for (int jj = 0; jj < 2; ++jj) {
@@ -478,7 +493,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                     float f[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v8[e]);
-                    if (dl == 0) {
+                    if (dl == 0 && !KO(1)) {
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
                             const int row = r0 + ((e & 2) ? 8 : 0);
@@ -496,7 +511,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             }
         }
         // ---- state update in registers and its bf16 operand copy for the next chunk
-        {
+        if (!KO(6)) {
             uint32_t v16[16];
             tmem_ld_16x256b_x4(tmS + wl + cb, v16);
             tmem_wait_ld();
@@ -535,7 +550,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         WKV6_TSTAMP(ic, 8);
 
         // ---- y epilogue: round to bf16 into the (now free) A tile, one TMA store per chunk
-        {
+        if (!KO(7)) {
             uint32_t v16[16];
             tmem_ld_16x256b_x4(tmY + wl + cb, v16);
             tmem_wait_ld();
