@@ -5,6 +5,11 @@
 //   A[t][s]  = sum_i r_t[i] k_s[i] exp(c_{t-1}[i] - c_s[i])      (s < t),   A[t][t] = sum_i r_t[i] u[i] k_t[i]
 //   y_t      = sum_s A[t][s] v_s  +  sum_i r_t[i] exp(c_{t-1}[i]) S_in[i][:]
 //   S_out    = diag(exp(c_63)) S_in + sum_s (k_s exp(c_63 - c_s)) (x) v_s
+// With a single reference point the diagonal of A (the bonus term) also comes from the tensor core: the operand
+// q_t = r_t u exp(c_t - c_rho) times k~_t gives sum_i r_t[i] u[i] k_t[i] on the diagonal of q k~^T (only the diagonal
+// blocks are read), and the factor exp(c_63 - c_rho) of the state increment is applied to the rows of the fp32
+// accumulator of k~^T v instead of to a second copy of k~.  With per-block reference points that factor differs from
+// block to block, so those chunks keep the copy k^ = k~ exp(c_63 - c_rho(J)) and sum the bonus on the CUDA cores.
 // The decay exponent of A is split between the two bf16 operands around reference points so that no factor
 // can overflow: tokens are grouped in blocks of 16, each block I has the reference rho_I = its 8th token, and
 //   r~_t = r_t exp(c_{t-1} - c_rho(I)),   k~_s = k_s exp(c_rho(J) - c_s),
@@ -16,7 +21,7 @@
 // kWideLimit2; the usual case) use the middle of the chunk as the single reference point and skip the copies.
 //
 // Tensor-memory map (256 columns, M = 64 accumulators occupy 16 lanes of each 32-lane quarter):
-//   lanes  0-15: cols [0,64) A for distance 0 | [64,128) y | [128,192) K^T V (state increment)
+//   lanes  0-15: cols [0,64) A for distance 0 | [64,128) y | [128,192) k~^T V (state increment) | [192,256) q k~^T (bonus)
 //   lanes 16-31: cols [0,48) A distance 1 | [48,80) distance 2 | [80,96) distance 3
 #pragma once
 
@@ -65,14 +70,15 @@ __device__ long long g_chunk_timing[64][16][8];
 struct ChunkFwdSmem {
     static constexpr int kStage = 4 * kTile;                 // r, k, v, w
     static constexpr int oStage0 = 0;
-    static constexpr int oKH = 2 * kStage;                   // k^ (decayed to the chunk end), MN-major A operand
+    static constexpr int oKH = 2 * kStage;                   // q = r u exp(c_t - c_rho), operand of the bonus product (per-block mode: k^)
     static constexpr int oKD = oKH + kTile;                  // k~ copies for block distances 1..3: 96 rows
     static constexpr int oAM = oKD + 96 * 128;               // masked A (bf16), later the y tile
     static constexpr int oSB = oAM + kTile;                  // bf16 copy of the state, MN-major B operand
     static constexpr int oHead = oSB + kTile;                // float [4][64]: log-decay sum of the first 8 tokens of a block
     static constexpr int oTot = oHead + 4 * 64 * 4;          // float [4][64]: log-decay sum of the block
     static constexpr int oDtot = oTot + 4 * 64 * 4;          // float [64]: decay over the whole chunk
-    static constexpr int oBonus = oDtot + 64 * 4;            // float [64]: sum_i r u k per token
+    static constexpr int oFK = oDtot + 64 * 4;               // float [64]: exp(c_63 - c_rho), scales the state increment rows
+    static constexpr int oBonus = oFK + 64 * 4;              // float [64]: sum_i r u k per token (per-block mode only)
     static constexpr int oBar = oBonus + 64 * 4;             // mbarriers: full[2], mma1, mma2
     static constexpr int oSlot = oBar + 4 * 8;
     static constexpr int kBytes = oSlot + 16;
@@ -158,6 +164,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     float *sHead = reinterpret_cast<float *>(smem + SM::oHead);  // [4][64] log2-decay sum of tokens 0..7 of a block
     float *sTail = reinterpret_cast<float *>(smem + SM::oTot);   // [4][64] log2-decay sum of tokens 8..15 of a block
     float *sDtot = reinterpret_cast<float *>(smem + SM::oDtot);
+    float *sFK = reinterpret_cast<float *>(smem + SM::oFK);
     float *sBonus = reinterpret_cast<float *>(smem + SM::oBonus);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SM::oBar);
     uint64_t *bar_full = bars, *bar_mma1 = bars + 2, *bar_mma2 = bars + 3;
@@ -213,12 +220,14 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                                      : make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane),
                                                    load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane + 1));
 
+    const __nv_bfloat162 ub = to_bf2(u2);
+
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tb = *slot;
-    const uint32_t tmA0 = tb, tmY = tb + 64, tmS = tb + 128, tmAD = tb + (16u << 16);
+    const uint32_t tmA0 = tb, tmY = tb + 64, tmS = tb + 128, tmAU = tb + 192, tmAD = tb + (16u << 16);
     const uint32_t wl = (uint32_t)(w4 * 32) << 16;  // this warp's TMEM lane quarter
     const uint32_t cb = 8 * n0;                     // first accumulator column of this thread's fragment
     // byte offsets of this thread's fragment elements (rows ta / ta+8, column pairs 8(n0+nn)+2q) in a swizzled tile
@@ -292,10 +301,10 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 const uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
                 const float2 w2 = ld_bf2(pt + 3 * kTile);
                 const float2 e2 = mul2(w2, make_float2(kLog2e, kLog2e));
-                float2 l2 = KO(3) ? make_float2(-0.5f, -0.5f) : mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
+                float2 l2 = mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
                 l2.x = fmaxf(l2.x, kMinLogDecay2);
                 l2.y = fmaxf(l2.y, kMinLogDecay2);
-                if (!KO(3) && !full_chunk && c * kChunk + 16 * w4 + 8 * half + tt >= a.T) l2 = make_float2(0.f, 0.f);
+                if (!full_chunk && c * kChunk + 16 * w4 + 8 * half + tt >= a.T) l2 = make_float2(0.f, 0.f);
                 cs = add2(cs, l2);
                 x[tt] = cs;
             }
@@ -329,7 +338,6 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             const float2 gstart = half ? add2(pre, head) : pre;  // running sum before this thread's first token
             const float2 nbase = make_float2(gstart.x - ref.x, gstart.y - ref.y);
             const __nv_bfloat162 fR = to_bf2(make_float2(ex2f(ref.x), ex2f(ref.y)));
-            const __nv_bfloat162 fK = to_bf2(make_float2(ex2f(all.x - ref.x), ex2f(all.y - ref.y)));
             // factors of the k~ copies for block distances 1..3 (only those with w4 + delta <= 3 exist)
             // (a factor can lie below the bf16 range while its product with k~ <= 2^115 does not: it is applied in two parts)
             __nv_bfloat162 fD[3], fE[3];
@@ -353,11 +361,11 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 *reinterpret_cast<float2 *>(&sDtot[2 * lane]) = make_float2(ex2f(all.x), ex2f(all.y));
                 dsum = add2(dsum, all);
             }
-            float bon[8];
+            const float2 fK = make_float2(ex2f(all.x - ref.x), ex2f(all.y - ref.y));  // decay from the reference point to the chunk end
+            if (warp == 4) *reinterpret_cast<float2 *>(&sFK[2 * lane]) = wide ? fK : make_float2(1.f, 1.f);
             const int kdo = (int)(sKD - sR), kho = (int)(sKH - sR);  // uniform offsets of the copy tiles from this stage
             // all loads first: shared-memory loads cannot be scheduled across the stores below
             __nv_bfloat162 rbv[8], kbv[8];
-            if (!KO(8)) {
 #pragma unroll
             for (int tt = 0; tt < 8; ++tt) {
                 const uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
@@ -366,40 +374,76 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             }
             // One straight-line block for all eight tokens (no branch inside: the scheduler interleaves the eight
             // dependency chains exp -> round -> scale -> store); the copies of the rare per-block mode follow separately.
-            __nv_bfloat162 ktv[8], rtv[8];
+            // feb[tt] = e^{c_{t-1} - c_ref} for this thread's token tt; feb[tt + 1] is at the same time e^{c_t - c_ref},
+            // the inverse of the factor of k~_t, which turns r_t u into the operand of the bonus product.
+            __nv_bfloat162 ktv[8], rtv[8], feb[9];
             {
-                float2 fe[8], fk2[8];
+                float2 fe[9], fk2[8];
 #pragma unroll
                 for (int tt = 0; tt < 8; ++tt) {  // exponents, then all exponentials back to back
                     const float2 xp = (tt == 0) ? make_float2(0.f, 0.f) : x[tt - 1];
                     fe[tt] = add2(xp, nbase);                                              // c_{t-1} - c_ref
                     fk2[tt] = make_float2(-nbase.x - x[tt].x, -nbase.y - x[tt].y);         // c_ref - c_t
                 }
+                fe[8] = add2(x[7], nbase);
+#pragma unroll
+                for (int tt = 0; tt < 9; ++tt) feb[tt] = to_bf2(make_float2(ex2f(fe[tt].x), ex2f(fe[tt].y)));
 #pragma unroll
                 for (int tt = 0; tt < 8; ++tt) {
-                    if (!KO(4)) {
-                    fe[tt] = make_float2(ex2f(fe[tt].x), ex2f(fe[tt].y));
                     fk2[tt] = make_float2(ex2f(fk2[tt].x), ex2f(fk2[tt].y));
-                    }
-                }
-#pragma unroll
-                for (int tt = 0; tt < 8; ++tt) {
-                    const __nv_bfloat162 rb = rbv[tt], kb = kbv[tt];
-                    const float2 rk = mul2(__bfloat1622float2(rb), __bfloat1622float2(kb));
-                    bon[tt] = KO(0) ? 0.f : fmaf(rk.x, u2.x, rk.y * u2.y);
-                    rtv[tt] = __hmul2(rb, to_bf2(fe[tt]));
-                    ktv[tt] = __hmul2(kb, to_bf2(fk2[tt]));
+                    rtv[tt] = __hmul2(rbv[tt], feb[tt]);
+                    ktv[tt] = __hmul2(kbv[tt], to_bf2(fk2[tt]));
                 }
             }
 #pragma unroll
             for (int tt = 0; tt < 8; ++tt) {
                 uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
                 *reinterpret_cast<__nv_bfloat162 *>(pt) = rtv[tt];                                  // r~
-                if (!KO(2)) *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rtv[tt], fR);         // r^ (over w)
+                *reinterpret_cast<__nv_bfloat162 *>(pt + 3 * kTile) = __hmul2(rtv[tt], fR);         // r^ (over w)
                 *reinterpret_cast<__nv_bfloat162 *>(pt + kTile) = ktv[tt];                          // k~ distance 0
-                if (!KO(2)) *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(ktv[tt], fK);               // k^
+                if (wide) *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(__hmul2(rbv[tt], ub), feb[tt + 1]);  // q
             }
             if (!wide) {
+                const __nv_bfloat162 fKb = to_bf2(fK);
+                float bon[8];
+#pragma unroll
+                for (int tt = 0; tt < 8; ++tt) {
+                    uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
+                    *reinterpret_cast<__nv_bfloat162 *>(pt + kho) = __hmul2(ktv[tt], fKb);  // k^
+                    const float2 rk = mul2(__bfloat1622float2(rbv[tt]), __bfloat1622float2(kbv[tt]));
+                    bon[tt] = fmaf(rk.x, u2.x, rk.y * u2.y);
+                }
+                // sum the bonus partials over the 32 channel pairs: 8 values across 32 lanes in 9 shuffles
+                {
+                    const bool up = (lane & 16) != 0;
+#pragma unroll
+                    for (int i2 = 0; i2 < 4; ++i2) {
+                        const float send = up ? bon[i2] : bon[i2 + 4];
+                        const float keep = up ? bon[i2 + 4] : bon[i2];
+                        bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+                    }
+                }
+                {
+                    const bool up = (lane & 8) != 0;
+#pragma unroll
+                    for (int i2 = 0; i2 < 2; ++i2) {
+                        const float send = up ? bon[i2] : bon[i2 + 2];
+                        const float keep = up ? bon[i2 + 2] : bon[i2];
+                        bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                    }
+                }
+                {
+                    const bool up = (lane & 4) != 0;
+                    const float send = up ? bon[0] : bon[1];
+                    const float keep = up ? bon[1] : bon[0];
+                    bon[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                }
+                bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 2);
+                bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 1);
+                if ((lane & 3) == 0) {
+                    const int tok = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                    sBonus[16 * w4 + 8 * half + tok] = bon[0];
+                }
 #pragma unroll
                 for (int tt = 0; tt < 8; ++tt) {
                     uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
@@ -408,40 +452,6 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                     if (w4 <= 1) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 48 * 128) = __hmul2(__hmul2(kt, fD[1]), fE[1]);   // rows [48,80)
                     if (w4 == 0) *reinterpret_cast<__nv_bfloat162 *>(pt + kdo + 80 * 128) = __hmul2(__hmul2(kt, fD[2]), fE[2]);   // rows [80,96)
                 }
-            }
-            }
-            if (!KO(0) && !KO(8)) {
-            // sum the bonus partials over the 32 channel pairs: 8 values across 32 lanes in 9 shuffles
-            {
-                const bool up = (lane & 16) != 0;
-#pragma unroll
-                for (int i2 = 0; i2 < 4; ++i2) {
-                    const float send = up ? bon[i2] : bon[i2 + 4];
-                    const float keep = up ? bon[i2 + 4] : bon[i2];
-                    bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-                }
-            }
-            {
-                const bool up = (lane & 8) != 0;
-#pragma unroll
-                for (int i2 = 0; i2 < 2; ++i2) {
-                    const float send = up ? bon[i2] : bon[i2 + 2];
-                    const float keep = up ? bon[i2 + 2] : bon[i2];
-                    bon[i2] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-                }
-            }
-            {
-                const bool up = (lane & 4) != 0;
-                const float send = up ? bon[0] : bon[1];
-                const float keep = up ? bon[1] : bon[0];
-                bon[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-            }
-            bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 2);
-            bon[0] += __shfl_xor_sync(0xffffffffu, bon[0], 1);
-            if ((lane & 3) == 0) {
-                const int tok = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                sBonus[16 * w4 + 8 * half + tok] = bon[0];
-            }
             }
         }
         fence_proxy_async_smem();
@@ -457,12 +467,17 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // A (distances 1..3) = r~ [k~ copies]^T
                 if (!wide) umma_ss(tmAD, dR + so + 2 * kk, dKD + 2 * kk, idKK96, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)  // q k~^T: its diagonal is the bonus sum_i r u k of every token
+                if (wide) umma_ss(tmAU, dKH + 2 * kk, dK + so + 2 * kk, idKK, kk > 0);
             umma_commit(bar_mma1);
         } else if (tid == 64) {
             tc_fence_after_sync();
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // state increment = k^^T v   (reverse-state mode: r^^T x2, r^ sits in the w tile)
-                umma_ss(tmS, (a.reverse_state ? dW + so : dKH) + 128 * kk, dV + so + 128 * kk, idMM, kk > 0);
+            // state increment = k~^T v with its rows scaled afterwards, or k^^T v (reverse-state mode: r^^T x2, r^ sits in the w tile)
+            const uint64_t dInc = a.reverse_state ? dW + so : (wide ? dK + so : dKH);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) umma_ss(tmS, dInc + 128 * kk, dV + so + 128 * kk, idMM, kk > 0);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // y = r^ S_in
                 umma_ss(tmY, dW + so + 2 * kk, dSB + 128 * kk, idKM, kk > 0);
@@ -475,9 +490,9 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
 
         // ---- epilogue of the intra-chunk matrix: pick, mask, round, store as the A operand of A v.
         // This warp covers column blocks J = 2*half and 2*half + 1 of row block I = w4.
-        const float bonus_a = sBonus[ta], bonus_b = sBonus[ta + 8];
         const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
-        if (!KO(5)) {
+        const float g0 = a.reverse_state ? 1.f : sFK[ta], g1 = a.reverse_state ? 1.f : sFK[ta + 8];
+        {
             const int I = w4;
 #pragma unroll
             for (int jj = 0; jj < 2; ++jj) {
@@ -493,13 +508,25 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                     float f[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v8[e]);
-                    if (dl == 0 && !KO(1)) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const int row = r0 + ((e & 2) ? 8 : 0);
-                            const int col = 8 * (e >> 2) + 2 * q + (e & 1);
-                            f[e] = (col < row) ? f[e] : (col == row ? ((e & 2) ? bonus_b : bonus_a) : 0.f);
+                    if (dl == 0) {
+                        // diagonal block: rows r0 (e = 0, 1, 4, 5) and r0 + 8 (e = 2, 3, 6, 7), columns 2q + (e & 1) (+ 8 for
+                        // e >= 4).  e = 2, 3 lie below the diagonal, e = 4, 5 above it; the other four need the test, and the
+                        // diagonal element itself comes from the bonus product.
+                        uint32_t b8[8];
+                        if (wide) {
+                            tmem_ld_16x256b_x2(tmAU + wl + 16 * J, b8);
+                            tmem_wait_ld();
+                        } else {
+                            b8[0] = b8[1] = __float_as_uint(sBonus[ta]);
+                            b8[6] = b8[7] = __float_as_uint(sBonus[ta + 8]);
                         }
+                        const int c0 = 2 * q, c1 = 2 * q + 1;
+                        f[0] = (c0 < r0) ? f[0] : (c0 == r0 ? __uint_as_float(b8[0]) : 0.f);
+                        f[1] = (c1 < r0) ? f[1] : (c1 == r0 ? __uint_as_float(b8[1]) : 0.f);
+                        f[6] = (c0 < r0) ? f[6] : (c0 == r0 ? __uint_as_float(b8[6]) : 0.f);
+                        f[7] = (c1 < r0) ? f[7] : (c1 == r0 ? __uint_as_float(b8[7]) : 0.f);
+                        f[4] = 0.f;
+                        f[5] = 0.f;
                     }
                     o0 = pack_bf2(f[0], f[1]); o2 = pack_bf2(f[2], f[3]);
                     o1 = pack_bf2(f[4], f[5]); o3 = pack_bf2(f[6], f[7]);
@@ -511,16 +538,16 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             }
         }
         // ---- state update in registers and its bf16 operand copy for the next chunk
-        if (!KO(6)) {
+        {
             uint32_t v16[16];
             tmem_ld_16x256b_x4(tmS + wl + cb, v16);
             tmem_wait_ld();
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
-                S[4 * nn + 0] = fmaf(S[4 * nn + 0], d0, __uint_as_float(v16[4 * nn + 0]));
-                S[4 * nn + 1] = fmaf(S[4 * nn + 1], d0, __uint_as_float(v16[4 * nn + 1]));
-                S[4 * nn + 2] = fmaf(S[4 * nn + 2], d1, __uint_as_float(v16[4 * nn + 2]));
-                S[4 * nn + 3] = fmaf(S[4 * nn + 3], d1, __uint_as_float(v16[4 * nn + 3]));
+                S[4 * nn + 0] = fmaf(S[4 * nn + 0], d0, g0 * __uint_as_float(v16[4 * nn + 0]));
+                S[4 * nn + 1] = fmaf(S[4 * nn + 1], d0, g0 * __uint_as_float(v16[4 * nn + 1]));
+                S[4 * nn + 2] = fmaf(S[4 * nn + 2], d1, g1 * __uint_as_float(v16[4 * nn + 2]));
+                S[4 * nn + 3] = fmaf(S[4 * nn + 3], d1, g1 * __uint_as_float(v16[4 * nn + 3]));
                 *reinterpret_cast<uint32_t *>(sSB + foA[nn]) = pack_bf2(S[4 * nn], S[4 * nn + 1]);
                 *reinterpret_cast<uint32_t *>(sSB + foB[nn]) = pack_bf2(S[4 * nn + 2], S[4 * nn + 3]);
             }
@@ -550,7 +577,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         WKV6_TSTAMP(ic, 8);
 
         // ---- y epilogue: round to bf16 into the (now free) A tile, one TMA store per chunk
-        if (!KO(7)) {
+        {
             uint32_t v16[16];
             tmem_ld_16x256b_x4(tmY + wl + cb, v16);
             tmem_wait_ld();
