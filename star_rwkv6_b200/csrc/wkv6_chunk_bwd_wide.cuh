@@ -399,21 +399,32 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         {
             float f[16];
             tmem_ld_16x256b_x4(tmP + lo + cb, f);
+            // P is kept strictly below the diagonal; its diagonal vg_t = gy_t . v_t goes aside.  Column block J against this
+            // warp's row block I = w4 decides per eight columns; only inside the diagonal block do single elements differ
+            // (rows r0 / r0 + 8 against columns 2q, 2q + 1 of the first / second eight columns).
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
-                const int s0 = 8 * (n0 + nn) + 2 * q;  // columns s0, s0 + 1
-#pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int t = ta + 8 * hrow;
-                    float x0 = f[4 * nn + 2 * hrow], x1 = f[4 * nn + 2 * hrow + 1];
-                    if (!KO(6)) {
-                    if (s0 == t) sVG[t] = x0;
-                    if (s0 + 1 == t) sVG[t] = x1;
-                    x0 = (s0 < t) ? x0 : 0.f;
-                    x1 = (s0 + 1 < t) ? x1 : 0.f;
+                const int J = 2 * half + (nn >> 1);
+                float x00 = f[4 * nn], x01 = f[4 * nn + 1], x10 = f[4 * nn + 2], x11 = f[4 * nn + 3];  // row ta: x0*, row ta+8: x1*
+                if (J > w4) {
+                    x00 = x01 = x10 = x11 = 0.f;
+                } else if (J == w4) {
+                    const int c0 = 2 * q, c1 = 2 * q + 1;
+                    if ((nn & 1) == 0) {          // columns 0..7 of the block: row r0 + 8 lies below, row r0 needs the test
+                        if (c0 == r0) sVG[ta] = x00;
+                        if (c1 == r0) sVG[ta] = x01;
+                        x00 = (c0 < r0) ? x00 : 0.f;
+                        x01 = (c1 < r0) ? x01 : 0.f;
+                    } else {                      // columns 8..15: row r0 lies above, row r0 + 8 needs the test
+                        if (c0 == r0) sVG[ta + 8] = x10;
+                        if (c1 == r0) sVG[ta + 8] = x11;
+                        x10 = (c0 < r0) ? x10 : 0.f;
+                        x11 = (c1 < r0) ? x11 : 0.f;
+                        x00 = x01 = 0.f;
                     }
-                    *reinterpret_cast<uint32_t *>(sP + FO(nn, hrow)) = pack_bf2(x0, x1);
                 }
+                *reinterpret_cast<uint32_t *>(sP + FO(nn, 0)) = pack_bf2(x00, x01);
+                *reinterpret_cast<uint32_t *>(sP + FO(nn, 1)) = pack_bf2(x10, x11);
             }
             // A: this warp covers column blocks J = 2*half, 2*half+1 of row block I = w4
             if (!KO(7))
@@ -428,14 +439,14 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                     float g8[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) g8[e] = __uint_as_float(v8[e]);
-                    if (J == I) {
+                    if (J == I) {  // diagonal block: e = 2, 3 lie below the diagonal, e = 4, 5 above it, the others need the test
                         const float bonus_a = sBonus[ta] + sBonus[64 + ta], bonus_b = sBonus[ta + 8] + sBonus[72 + ta];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const int row = r0 + ((e & 2) ? 8 : 0);
-                            const int col = 8 * (e >> 2) + 2 * q + (e & 1);
-                            g8[e] = (col < row) ? g8[e] : (col == row ? ((e & 2) ? bonus_b : bonus_a) : 0.f);
-                        }
+                        const int c0 = 2 * q, c1 = 2 * q + 1;
+                        g8[0] = (c0 < r0) ? g8[0] : (c0 == r0 ? bonus_a : 0.f);
+                        g8[1] = (c1 < r0) ? g8[1] : (c1 == r0 ? bonus_a : 0.f);
+                        g8[6] = (c0 < r0) ? g8[6] : (c0 == r0 ? bonus_b : 0.f);
+                        g8[7] = (c1 < r0) ? g8[7] : (c1 == r0 ? bonus_b : 0.f);
+                        g8[4] = g8[5] = 0.f;
                     }
                     o0 = pack_bf2(g8[0], g8[1]); o2 = pack_bf2(g8[2], g8[3]);
                     o1 = pack_bf2(g8[4], g8[5]); o3 = pack_bf2(g8[6], g8[7]);
