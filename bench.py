@@ -5,9 +5,12 @@
     python bench.py --impl reference --gpus N --steps K ...  # the reference algorithm on the host cores
 
 One "step" is one forward plus one backward of the operator over one batch of seeded synthetic inputs
-(r,k,v ~ N(0,1)/sqrt(N), w ~ U(-6,1), u ~ N(0,0.1), gy ~ N(0,1)).  Every rank runs the full workload on
-its own GPU (weak scaling: the (batch, head) pairs are independent, so there is no data-path collective);
-``--scaling strong`` instead splits the B rows of the one workload across the ranks.
+(r,k,v ~ N(0,1)/sqrt(N), w ~ U(-6,1), u ~ N(0,0.1), gy ~ N(0,1)).  With N GPUs the one workload is split over the
+ranks by (batch, head) pairs, which are independent, so there is no data-path collective (``--scaling strong``, the
+default); every rank first checks its shard against the unsplit kernels on the same data and the verdict is part of
+the JSON line (``shard_check``), and a short run of the long-sequence workload (B1 T131072 H32, T sharded over the
+ranks, states carried rank to rank) is reported under ``long_sequence``.  ``--scaling weak`` instead runs the full
+workload on every rank.
 
 Rank 0 prints one JSON line.  ``value`` is device-resident throughput (CUDA events, max over ranks);
 ``e2e`` is the same step driven through ``RWKVKernelOperator`` from pinned host buffers with the host<->device
@@ -43,7 +46,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--variant", default="auto", choices=["auto", "seq", "chunk"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--B", type=int, default=8)
     ap.add_argument("--T", type=int, default=4096)
     ap.add_argument("--H", type=int, default=32)
@@ -69,6 +72,8 @@ def parse():
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step from Python instead of replaying CUDA graphs (one graph per kernel group and input set)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-long-sequence", action="store_true", help="skip the T-sharded long-sequence leg of multi-GPU runs")
+    ap.add_argument("--long-T", type=int, default=131072, help="sequence length of the long-sequence leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-heads", type=int, default=0, help="(b,h) pairs in the CPU sample; 0 = auto")
     return ap.parse_args()
@@ -253,6 +258,22 @@ class ClockSampler:
 
 # ---- GPU arm --------------------------------------------------------------------------------------
 
+def _scaled_err(a, b):
+    import torch
+    den = float(b.float().abs().max())
+    return float((a.float() - b.float()).abs().max()) / (den if den > 0 else 1.0)
+
+
+def _device_inputs(torch, dev, B, T, C, H, N, xdt, seed):
+    """One seeded input set, generated on the device (the same values on every rank for the same seed)."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    mk = lambda s: (torch.randn(B, T, C, generator=g, device=dev) * s).to(xdt)
+    d = {"r": mk(N ** -0.5), "k": mk(N ** -0.5), "v": mk(N ** -0.5),
+         "w": (torch.rand(B, T, C, generator=g, device=dev) * 7.0 - 6.0).to(xdt), "gy": mk(1.0)}
+    u = torch.randn(H, N, generator=g, device=dev) * 0.1
+    return d, u
+
+
 def run_b200(a):
     import torch
     import torch.distributed as dist
@@ -269,50 +290,54 @@ def run_b200(a):
         dist.init_process_group("nccl", device_id=dev)
 
     import star_rwkv6_b200 as pkg
-    from star_rwkv6_b200 import _lib
+    from star_rwkv6_b200 import _lib, segments as seg, sharding
     from star_rwkv6_b200.rwkv_kernel.torch_rwkv_kernel import RWKVKernelOperator
 
-    B, T, H, N = a.B, a.T, a.H, a.N
+    N = a.N
+    xdt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    variant = _lib.VARIANTS[a.variant]
+    strong = a.scaling == "strong" and world > 1 and not a.tshard
+    plan = sharding.make_plan(a.B, a.H, world) if strong else None
+    B, T, H = a.B, a.T, a.H
     if a.tshard and world > 1:
         assert T % world == 0
         T = T // world                                            # each rank holds a contiguous T range
-    elif a.scaling == "strong" and world > 1:
-        from star_rwkv6_b200 import sharding
-        B, H = sharding.make_plan(a.B, a.H, world).local_shape()  # each rank generates its own shard directly
+    elif strong:
+        B, H = plan.local_shape()
     C = H * N
+    chunk_ok = a.dtype == "bf16" and N == 64 and a.variant != "seq"
     if a.segments == 0:
-        from star_rwkv6_b200.segments import auto_segments
-        a.segments = auto_segments(B, T, H) if (a.dtype == "bf16" and N == 64 and a.variant != "seq") else 1
-    xdt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
-    variant = _lib.VARIANTS[a.variant]
+        a.segments = seg.auto_segments(B, T, H) if chunk_ok else 1
 
-    # seeded synthetic inputs, generated on the host; two rotating sets so consecutive steps do not reuse lines
-    g = torch.Generator().manual_seed(1234 + (rank if a.scaling == "strong" else 0))
+    # Seeded synthetic inputs, generated on the device; two rotating sets so that consecutive steps do not reuse cache
+    # lines.  A split run generates the whole workload on every rank (same seed, same values) and keeps its shard.
     nsets = 2
-    host, devs = [], []
-    for s in range(nsets):
-        hs = {
-            "r": (torch.randn(B, T, C, generator=g) / N ** 0.5).to(xdt).pin_memory(),
-            "k": (torch.randn(B, T, C, generator=g) / N ** 0.5).to(xdt).pin_memory(),
-            "v": (torch.randn(B, T, C, generator=g) / N ** 0.5).to(xdt).pin_memory(),
-            "w": (torch.rand(B, T, C, generator=g) * 7.0 - 6.0).to(xdt).pin_memory(),
-            "gy": torch.randn(B, T, C, generator=g).to(xdt).pin_memory(),
-        }
-        host.append(hs)
-        devs.append({n: t.to(dev) for n, t in hs.items()})
-    u_host = (torch.randn(H, N, generator=g) * 0.1).pin_memory()
-    u = u_host.to(dev)
+    devs, globals0 = [], None
+    for sidx in range(nsets):
+        if strong:
+            gd, gu_ = _device_inputs(torch, dev, a.B, a.T, a.H * N, a.H, N, xdt, 1234 + sidx)
+            devs.append({n: x.contiguous() for n, x in zip(("r", "k", "v", "w", "gy"),
+                                                          sharding.shard(plan, rank, N, *(gd[n] for n in ("r", "k", "v", "w", "gy"))))})
+            u = sharding.shard_u(plan, rank, gu_).contiguous()
+            if sidx == 0:
+                globals0 = (gd, gu_)
+            del gd
+        else:
+            d, u = _device_inputs(torch, dev, B, T, C, H, N, xdt, 1234 + sidx)   # T-sharded runs: every rank its own range
+            devs.append(d)
+    host = [{n: t.cpu().pin_memory() for n, t in d.items()} for d in devs]
+    u_host = u.cpu().pin_memory()
 
     resolved = pkg.ops.resolve_variant(devs[0]["r"], u, N, variant)
     vname = {1: "seq", 2: "chunk"}[resolved]
     launches_per_step = {"seq": 4, "chunk": 3}[vname]  # chunk: forward, fast backward, general backward (exits at once when nothing is flagged)
     segmented = a.segments > 1 or (a.tshard and world > 1)
+    collective = a.tshard and world > 1
     if segmented:
-        from star_rwkv6_b200 import segments as seg
         assert vname == "chunk", "sequence splitting uses the chunked kernels"
-        be = seg.LibraryBackend(N)
-        grp = dist.group.WORLD if (a.tshard and world > 1) else None
-        launches_per_step = 7  # summary + scan + kernel(s), forward and backward
+        be = seg.LibraryBackend(N, reuse_buffers=not collective)
+        grp = dist.group.WORLD if collective else None
+        launches_per_step = 8  # forward: summary, scan, kernel; backward: summary, scan, fast + general kernel, gu row sum
 
         def step(d):
             y, _, ctx = seg.segmented_forward(be, d["r"], d["k"], d["v"], d["w"], u, a.segments, want_ckpt=True, group=grp)
@@ -327,6 +352,38 @@ def run_b200(a):
 
         def step_bwd(d, ckpt):
             return pkg.backward_raw(d["r"], d["k"], d["v"], d["w"], u, d["gy"], N, ckpt=ckpt, variant=variant)
+
+    # ---- a split run first proves its split: the shard's results against the unsplit kernels on the whole workload
+    shard_check = None
+    if strong:
+        gd, gu_ = globals0
+        yg, _, ckg = pkg.forward_raw(gd["r"], gd["k"], gd["v"], gd["w"], gu_, N, want_ckpt=True, variant=variant)
+        gg = pkg.backward_raw(gd["r"], gd["k"], gd["v"], gd["w"], gu_, gd["gy"], N, ckpt=ckg, variant=variant)
+        bs, cs = plan.batch_slice(rank), plan.channel_slice(rank, N)
+        want = [yg[bs, :, cs]] + [x[bs, :, cs] for x in gg[:4]]
+        gu_ref = gg[4][bs].sum(0)[plan.head_slice(rank)]
+        d0 = devs[0]
+        # (1) the shard through the same kernels, one piece per sequence: bit for bit the slice of the whole run
+        y1, _, ck1 = pkg.forward_raw(d0["r"], d0["k"], d0["v"], d0["w"], u, N, want_ckpt=True, variant=variant)
+        g1 = pkg.backward_raw(d0["r"], d0["k"], d0["v"], d0["w"], u, d0["gy"], N, ckpt=ck1, variant=variant)
+        bit_equal = all(torch.equal(x, y_) for x, y_ in zip([y1, *g1[:4]], want)) and torch.equal(g1[4].sum(0), gu_ref)
+        # (2) the step that is timed (its sequences cut into segments when the shard alone cannot fill the GPU)
+        ys, ck = step(d0)
+        gs = step_bwd(d0, ck)
+        torch.cuda.synchronize()
+        gu_got = gs[4] if gs[4].dim() == 2 else gs[4].sum(0)
+        worst = max([_scaled_err(x, y_) for x, y_ in zip([ys, *gs[:4]], want)] + [_scaled_err(gu_got, gu_ref)])
+        status = _lib.lib.wkv6_device_status()
+        flags = torch.tensor([1.0 if bit_equal else 0.0, 1.0 if (worst <= 1e-2 and status == 0) else 0.0, -worst], device=dev,
+                             dtype=torch.float64)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        shard_check = {"bxh_bit_equal": bool(flags[0].item() == 1.0),
+                       "timed_step_within_1e-2_of_unsplit": bool(flags[1].item() == 1.0), "max_scaled_err": -flags[2].item(),
+                       "against": "forward + backward of the whole workload through the unsplit kernels on every rank, "
+                                  "compared on the rank's (batch, head) shard: y, gr, gk, gv, gw, gu",
+                       "segments_per_sequence_in_timed_step": a.segments}
+        del gd, gu_, yg, ckg, gg, ys, ck, gs, globals0, want, y1, ck1, g1
+        torch.cuda.empty_cache()
 
     # clocks are sampled from the warm-up on: the timed region itself can be shorter than one sampling period
     sampler = ClockSampler(local) if rank == 0 else None
@@ -345,14 +402,17 @@ def run_b200(a):
 
     # The timed steps replay CUDA graphs (forward and backward captured separately per input set, so that the events
     # between them stay outside the graphs): a step then costs the host three event records and two replays, and a
-    # busy host cannot stretch the measured kernels.  Segmented / sharded-T runs contain collectives and stay eager.
+    # busy host cannot stretch the measured kernels.  Runs with a collective inside the step (T sharded over ranks)
+    # stay eager.
     graphs = None
-    if not a.no_graph and not segmented:
+    if not a.no_graph and not collective:
         graphs = []
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for d in devs:
+                if segmented:
+                    be = seg.LibraryBackend(N, reuse_buffers=True)   # one buffer set per captured input set
                 gf = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gf, stream=side):
                     y, ck = step(d)
@@ -391,14 +451,15 @@ def run_b200(a):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, fwd_ms, bwd_ms = t.tolist()
     ms_per_step = total_ms / a.steps
-    tokens_per_step_global = B * T * world  # every rank processes B*T tokens of H heads
-    if (a.scaling == "strong" or a.tshard) and world > 1:
+    tokens_per_step_global = B * T * world  # weak scaling: every rank processes B*T tokens of H heads
+    if (strong or a.tshard) and world > 1:
         tokens_per_step_global = a.B * a.T
     value = tokens_per_step_global / (ms_per_step * 1e-3) / 1e6
+    device_status = _lib.lib.wkv6_device_status()
 
     # e2e: through the operator, host buffers, copies inside the timed region
     e2e = None
-    if not a.no_e2e and not segmented:
+    if not a.no_e2e and not collective:
         op = RWKVKernelOperator(N, T, variant=a.variant)
         ydt = xdt
         out_host = {n: torch.empty(B, T, C, dtype=ydt).pin_memory() for n in ("y", "gr", "gk", "gv", "gw")}
@@ -448,48 +509,137 @@ def run_b200(a):
         e2e = {"value": tokens_per_step_global / (e2e_ms * 1e-3) / 1e6, "unit": UNIT,
                "h2d_bytes_per_step": 5 * B * T * C * esz + H * N * 4,
                "d2h_bytes_per_step": 5 * B * T * C * esz + H * N * 4,
+               "bytes_are": "per rank",
                "ms_per_step": e2e_ms, "steps": n_e2e,
                "api": "star_rwkv6_b200.host.HostPipeline.fwd_bwd on pinned host tensors (batch rows streamed, both copy directions "
                       "and the kernels overlapped)",
                "operator_on_device_copies": {"value": tokens_per_step_global / (op_ms * 1e-3) / 1e6, "ms_per_step": op_ms,
                                              "api": "copy everything in, RWKVKernelOperator.__call__ + backward, copy everything out"}}
+        del pipe, out_host
+
+    # ---- multi-GPU runs add a short leg of the long-sequence workload, T sharded over the ranks
+    long_seq = None
+    launch_mode = "CUDA graph replays (forward, backward)" if graphs is not None else "eager launches"
+    if world > 1 and not a.no_long_sequence and not a.tshard and chunk_ok:
+        del devs, host, graphs, y, ck, grads
+        torch.cuda.empty_cache()
+        long_seq = long_sequence_leg(a, torch, dist, pkg, seg, dev, rank, world, N)
 
     if rank == 0:
         peak, peak_src = measured_peak()
         esz = 2 if a.dtype == "bf16" else 4
-        elems = B * T * C
+        elems = B * T * C          # per rank
         bwd_bytes, fwd_bytes = 9 * esz * elems, 5 * esz * elems
-        # dram__bytes_read.sum + dram__bytes_write.sum per (token, channel) of the chunked backward, from the ncu
-        # capture summarised under profiles/ (it scales with the number of (batch, head) sequences)
-        traffic = 17.9 * elems if (vname == "chunk" and a.dtype == "bf16" and not segmented) else None
+        # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch: per (token, channel) figure of the ncu
+        # capture whose summary sits beside it (traffic grows in proportion to the (batch, head) sequences)
+        traffic = None
+        per_elem = profiled_traffic_per_element()
+        if per_elem is not None and vname == "chunk" and a.dtype == "bf16" and not segmented:
+            traffic = per_elem * elems
         achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
         roofline = {
             "bound": "hbm", "kernel": f"{vname} backward", "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
-            "algorithmic_bytes_per_launch": bwd_bytes, "avg_ms": bwd_ms,
+            "algorithmic_bytes_per_launch": bwd_bytes, "avg_ms": bwd_ms, "figures_are": "per GPU",
             "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
                         "algorithmic_bytes_per_launch": fwd_bytes, "avg_ms": fwd_ms},
             "step": {"achieved": (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9,
                      "frac": (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9 / peak},
         }
         cpu = None if (a.no_cpu_baseline or world > 1) else cpu_baseline(a)  # a one-GPU figure
+        if collective:
+            par = f"T sharded over {world} ranks, states carried by all-gather + scan"
+        elif strong:
+            par = (f"one workload split over {world} ranks by (batch, head): {plan.batch_parts} batch x {plan.head_parts} head "
+                   "parts, no collective")
+        else:
+            par = f"{world} independent ranks, each the whole workload, no collective"
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(3, a.warmup),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if a.tshard else a.scaling, "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if (a.tshard or strong or world == 1 and a.scaling == "strong") else "weak", "vs_baseline": None,
             "dtype": "bf16" if a.dtype == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": workload_name(a), "per_gpu": f"B{B} T{T} H{H} N{N}", "variant": vname,
                        "u_dtype": "f32", "state": "f32",
-                       "l2": "two rotating input sets of 671 MB each, larger than the 126 MB L2",
+                       "l2": f"two rotating input sets of {5 * elems * esz / 1e6:.0f} MB each per GPU"
+                             + (", larger than the 126 MB L2" if 5 * elems * esz > 126e6 else " (smaller than the 126 MB L2: the split leaves each GPU less than one L2 of inputs)"),
                        "segments_per_sequence": a.segments,
-                       "launch": "CUDA graph replays (forward, backward)" if graphs is not None else "eager launches",
-                       "parallelism": (f"T sharded over {world} ranks, states carried by all-gather + scan" if (a.tshard and world > 1)
-                                       else f"{world} independent ranks over (batch, head), no collective")},
+                       "launch": launch_mode,
+                       "parallelism": par},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-            "gpu_launches": launches_per_step * a.steps,
+            "gpu_launches": launches_per_step * a.steps, "device_status": device_status,
         }
+        if shard_check is not None:
+            line["shard_check"] = shard_check
+        if long_seq is not None:
+            line["long_sequence"] = long_seq
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def long_sequence_leg(a, torch, dist, pkg, seg, dev, rank, world, N):
+    """B1 T131072 H32 bf16, T sharded over the ranks: per-head states carried rank to rank (all-gather of the segment
+    summaries over NCCL + scan), checked on every rank against the unsplit kernels run over the whole sequence."""
+    from star_rwkv6_b200 import _lib
+    B, T, H = 1, a.long_T, 32
+    C = H * N
+    Tl = T // world
+    gd, u = _device_inputs(torch, dev, B, T, C, H, N, torch.bfloat16, 4321)
+    sl = slice(rank * Tl, (rank + 1) * Tl)
+    loc = {n: x[:, sl].contiguous() for n, x in gd.items()}
+    G = seg.auto_segments(B, Tl, H)
+    be = seg.LibraryBackend(N)
+    grp = dist.group.WORLD
+
+    def step():
+        y, _, ctx = seg.segmented_forward(be, loc["r"], loc["k"], loc["v"], loc["w"], u, G, want_ckpt=True, group=grp)
+        return y, seg.segmented_backward(be, ctx, loc["r"], loc["k"], loc["v"], loc["w"], u, loc["gy"])
+
+    y, g = step()
+    # the single-GPU result: the same sequence in one piece on this rank (cut into segments inside the GPU only)
+    G1 = seg.auto_segments(B, T, H)
+    y1, _, ctx1 = seg.segmented_forward(be, gd["r"], gd["k"], gd["v"], gd["w"], u, G1, want_ckpt=True)
+    g1 = seg.segmented_backward(be, ctx1, gd["r"], gd["k"], gd["v"], gd["w"], u, gd["gy"])
+    torch.cuda.synchronize()
+    errs = [_scaled_err(y, y1[:, sl])] + [_scaled_err(x, x1[:, sl]) for x, x1 in zip(g[:4], g1[:4])] + [_scaled_err(g[4], g1[4])]
+    status = _lib.lib.wkv6_device_status()
+    flags = torch.tensor([1.0 if (max(errs) <= 1e-2 and status == 0) else 0.0, -max(errs)], device=dev, dtype=torch.float64)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    del y1, ctx1, g1, gd
+    torch.cuda.empty_cache()
+    for _ in range(3):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    steps = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    peak, _ = measured_peak()
+    return {"workload": f"wkv6 fwd+bwd B{B} T{T} H{H} N{N} bf16, T sharded over {world} ranks, {G} segments per rank",
+            "ms_per_step": ms, "value": B * T / (ms * 1e-3) / 1e6, "unit": UNIT, "steps": steps, "warmup": 3,
+            "roofline_step_frac": 28.0 * B * Tl * C / (ms * 1e-3) / 1e9 / peak,
+            "launch": "eager launches, NCCL all-gather of the summaries inside every step",
+            "matches_single_gpu": bool(flags[0].item() == 1.0), "max_scaled_err_vs_single_gpu": -flags[1].item(),
+            "against": "the same sequence through the kernels of one GPU (every rank runs it whole), all of y, gr, gk, gv, gw, gu"}
+
+
+def profiled_traffic_per_element():
+    """DRAM bytes per (token, channel) of one launch of the chunked backward, from the figure stored beside the ncu
+    summary it was captured for (profiles/chunk_backward_dram_bytes.json); None when that file is absent."""
+    path = os.path.join(ROOT, "profiles", "chunk_backward_dram_bytes.json")
+    try:
+        return float(json.load(open(path))["dram_bytes_per_token_channel"])
+    except (OSError, KeyError, ValueError):
+        return None
 
 
 def measured_peak():
@@ -802,7 +952,7 @@ def run_train_step(a):
 
 
 def run_inference(a):
-    """BASELINE's configuration 3: 7B-shape model (32 layers, d_model 4096, 64 heads of 64, ffn 14336, vocab
+    """The 7B-shape inference workload: (32 layers, d_model 4096, 64 heads of 64, ffn 14336, vocab
     65536, bf16, random init), prefill of B16 x T4096 random token ids, then greedy decode steps replayed from one CUDA
     graph, each carrying the per-layer [B,H,64,64] fp32 WKV states (updated in place by the decode kernel).
     With N GPUs the batch is sharded (B/N sequences per rank, weights replicated, no collective on the data path)."""

@@ -21,11 +21,26 @@ import torch.distributed as dist
 
 
 class LibraryBackend:
-    """Chunked sm_100a kernels through the C ABI (bf16 r,k,v,w,gy; N = 64)."""
+    """Chunked sm_100a kernels through the C ABI (bf16 r,k,v,w,gy; N = 64).
 
-    def __init__(self, head_size: int):
+    ``reuse_buffers=True`` keeps every output, summary, checkpoint and workspace buffer of the first call and hands the
+    same memory out again on later calls of the same shapes, so that a step allocates nothing (a training loop that
+    consumes the results of one step before it starts the next; results of an earlier call are overwritten)."""
+
+    def __init__(self, head_size: int, reuse_buffers: bool = False):
         from . import _lib, ops
         self.L, self.ops, self.N = _lib, ops, head_size
+        self.reuse = reuse_buffers
+        self._bufs = {}
+
+    def _buf(self, name, shape, dtype, device):
+        if not self.reuse:
+            return torch.empty(shape, dtype=dtype, device=device)
+        key = (name, tuple(shape), dtype, str(device))
+        t = self._bufs.get(key)
+        if t is None:
+            t = self._bufs[key] = torch.empty(shape, dtype=dtype, device=device)
+        return t
 
     def _problem(self, x, u=None):
         u = u if u is not None else torch.empty(0, dtype=torch.float32, device=x.device)
@@ -37,8 +52,9 @@ class LibraryBackend:
     def summary(self, x1, x2, w, reverse: bool):
         Bn, T, C = x1.shape
         H = C // self.N
-        state = torch.empty((Bn, H, self.N, self.N), dtype=torch.float32, device=x1.device)
-        dec = torch.empty((Bn, H, self.N), dtype=torch.float32, device=x1.device)
+        tag = "rev" if reverse else "fwd"
+        state = self._buf("sum_state_" + tag, (Bn, H, self.N, self.N), torch.float32, x1.device)
+        dec = self._buf("sum_dec_" + tag, (Bn, H, self.N), torch.float32, x1.device)
         p = self._problem(x1)
         ptr = self.ops._ptr
         with torch.cuda.device(x1.device):
@@ -47,8 +63,9 @@ class LibraryBackend:
         return state, dec
 
     def scan(self, B, H, G, dec, state, s0, reverse: bool):
-        out = torch.empty_like(state)
-        last = torch.empty((B, H, self.N, self.N), dtype=torch.float32, device=state.device)
+        tag = "rev" if reverse else "fwd"
+        out = self._buf("scan_out_" + tag, tuple(state.shape), torch.float32, state.device)
+        last = self._buf("scan_last_" + tag, (B, H, self.N, self.N), torch.float32, state.device)
         ptr = self.ops._ptr
         with torch.cuda.device(state.device):
             self.L.check(self.L.lib.wkv6_state_scan(B, H, self.N, G, ptr(dec), ptr(state), ptr(s0), ptr(out), ptr(last),
@@ -56,18 +73,29 @@ class LibraryBackend:
         return out, last
 
     def forward(self, r, k, v, w, u, s_in, want_ckpt: bool):
-        y, _, ckpt = self.ops.forward_raw(r, k, v, w, u, self.N, s_in=s_in, want_ckpt=want_ckpt, variant=self.L.VARIANT_CHUNK)
+        if not self.reuse:
+            y, _, ckpt = self.ops.forward_raw(r, k, v, w, u, self.N, s_in=s_in, want_ckpt=want_ckpt, variant=self.L.VARIANT_CHUNK)
+            return y, ckpt
+        Bn, T, C = r.shape
+        p = self.ops.make_problem(r, u, self.N, r.dtype, self.L.VARIANT_CHUNK)
+        y = self._buf("y", (Bn, T, C), r.dtype, r.device)
+        nbytes = self.L.lib.wkv6_ckpt_bytes(ctypes.byref(p)) if want_ckpt else 0
+        ckpt = self._buf("ckpt", (nbytes,), torch.uint8, r.device) if nbytes else None
+        ptr = self.ops._ptr
+        with torch.cuda.device(r.device):
+            self.L.check(self.L.lib.wkv6_forward(ctypes.byref(p), ptr(r), ptr(k), ptr(v), ptr(w), ptr(u), ptr(y), ptr(s_in), None,
+                                                 s_in.shape[0] if s_in is not None else 0, None, ptr(ckpt), self._stream(r)))
         return y, ckpt
 
     def backward(self, r, k, v, w, u, gy, ckpt, ab_in):
         Bn, T, C = r.shape
         H = C // self.N
         p = self.ops.make_problem(r, u, self.N, r.dtype, self.L.VARIANT_CHUNK)
-        g = [torch.empty_like(r) for _ in range(4)]
-        gu = torch.empty((Bn, H, self.N), dtype=torch.float32, device=r.device)
+        g = [self._buf("g" + n, (Bn, T, C), r.dtype, r.device) for n in "rkvw"]
+        gu = self._buf("gu", (Bn, H, self.N), torch.float32, r.device)
         ptr = self.ops._ptr
         nbytes = self.L.lib.wkv6_backward_workspace_bytes(ctypes.byref(p), 1)
-        ws = torch.empty((nbytes,), dtype=torch.uint8, device=r.device) if nbytes else None
+        ws = self._buf("ws", (nbytes,), torch.uint8, r.device) if nbytes else None
         with torch.cuda.device(r.device):
             self.L.check(self.L.lib.wkv6_backward_seeded(ctypes.byref(p), ptr(r), ptr(k), ptr(v), ptr(w), ptr(u), ptr(gy),
                                                          *(ptr(x) for x in g), ptr(gu), ptr(ckpt), ptr(ab_in), ptr(ws),
