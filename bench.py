@@ -318,13 +318,15 @@ def run_b200(a):
             gd, gu_ = _device_inputs(torch, dev, a.B, a.T, a.H * N, a.H, N, xdt, 1234 + sidx)
             devs.append({n: x.contiguous() for n, x in zip(("r", "k", "v", "w", "gy"),
                                                           sharding.shard(plan, rank, N, *(gd[n] for n in ("r", "k", "v", "w", "gy"))))})
-            u = sharding.shard_u(plan, rank, gu_).contiguous()
-            if sidx == 0:
+            if sidx == 0:   # one u for every input set
+                u = sharding.shard_u(plan, rank, gu_).contiguous()
                 globals0 = (gd, gu_)
             del gd
         else:
-            d, u = _device_inputs(torch, dev, B, T, C, H, N, xdt, 1234 + sidx)   # T-sharded runs: every rank its own range
+            d, u_ = _device_inputs(torch, dev, B, T, C, H, N, xdt, 1234 + sidx)  # T-sharded runs: every rank its own range
             devs.append(d)
+            if sidx == 0:
+                u = u_
     host = [{n: t.cpu().pin_memory() for n, t in d.items()} for d in devs]
     u_host = u.cpu().pin_memory()
 

@@ -5,6 +5,7 @@
 #include "wkv6_chunk_bwd.cuh"
 #include "wkv6_chunk_bwd_wide.cuh"
 #include "wkv6_chunk_fwd.cuh"
+#include "wkv6_chunk_summary.cuh"
 #include "wkv6_internal.h"
 
 namespace wkv6 {
@@ -141,7 +142,7 @@ int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, c
 
 // Summary of every sequence as an affine map of the state: log2 of the total decay per key channel and the state
 // the sequence builds from zero.  Forward direction: x1 = k, x2 = v.  Reverse direction (the backward's state):
-// x1 = r, x2 = gy.  It is the forward kernel with its y output suppressed.
+// x1 = r, x2 = gy.  A kernel of its own (wkv6_chunk_summary.cuh): one scaled operand and one product per chunk.
 int chunk_segment_summary(const wkv6_problem *p, const Dims &d, const void *x1, const void *x2, const void *w,
                           bool reverse, float *b_out, float *dec_log2_out, cudaStream_t st) {
     CUtensorMap m1, m2, mw;
@@ -152,12 +153,12 @@ int chunk_segment_summary(const wkv6_problem *p, const Dims &d, const void *x1, 
     ChunkFwdArgs a{};
     a.u = nullptr; a.u_dtype = WKV6_F32; a.s_dtype = WKV6_F32; a.s_out = b_out; a.B = p->B; a.T = p->T; a.H = p->H;
     a.write_y = false; a.reverse_state = reverse; a.dec_out = dec_log2_out;
-    cudaError_t e = cudaFuncSetAttribute(chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         ChunkFwdSmem::kAlloc);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_fwd_kernel)");
-    chunk_fwd_kernel<<<p->B * p->H, 256, ChunkFwdSmem::kAlloc, st>>>(m1, m1, m2, mw, m1, a);
+    cudaError_t e = cudaFuncSetAttribute(chunk_summary_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ChunkSumSmem::kAlloc);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_summary_kernel)");
+    chunk_summary_kernel<<<p->B * p->H, 256, ChunkSumSmem::kAlloc, st>>>(m1, m2, mw, a);
     e = cudaGetLastError();
-    return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_fwd_kernel (summary) launch");
+    return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_summary_kernel launch");
 }
 
 // Exclusive scan of affine state maps over the G segments of each sequence:
