@@ -215,7 +215,7 @@ def test_segmented_matches_unsplit(pkg, B, T, H, G):
     # and against the unsplit kernels: same inputs, only the association of the state products differs
     y1, s1, ck = pkg.forward_raw(t["r"], t["k"], t["v"], t["w"], t["u"], N, want_state=True, want_ckpt=True, variant=pkg.VARIANT_CHUNK)
     assert scaled_err(np_(y), np_(y1)) <= 1e-2
-    assert scaled_err(np_(last), np_(s1)) <= 5e-3
+    assert scaled_err(np_(last), np_(s1)) <= 1e-2   # two bf16 roundings of the operands apart (summary kernel / forward kernel)
 
 
 def test_segmented_autograd(pkg):
