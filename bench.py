@@ -72,6 +72,7 @@ def parse():
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step from Python instead of replaying CUDA graphs (one graph per kernel group and input set)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference's own CUDA kernels (one-GPU runs)")
     ap.add_argument("--no-long-sequence", action="store_true", help="skip the T-sharded long-sequence leg of multi-GPU runs")
     ap.add_argument("--long-T", type=int, default=131072, help="sequence length of the long-sequence leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -519,6 +520,13 @@ def run_b200(a):
                                              "api": "copy everything in, RWKVKernelOperator.__call__ + backward, copy everything out"}}
         del pipe, out_host
 
+    # ---- one GPU: the reference's own CUDA kernels on the first input set, beside this library's results for it
+    ref_cuda_res = None
+    if world == 1 and not segmented and vname == "chunk" and not a.no_reference_cuda:
+        yo, cko = step(devs[0])
+        ref_cuda_res = reference_cuda_leg(a, torch, pkg, devs[0], u, N, (yo, step_bwd(devs[0], cko)))
+        del yo, cko
+
     # ---- multi-GPU runs add a short leg of the long-sequence workload, T sharded over the ranks
     long_seq = None
     launch_mode = "CUDA graph replays (forward, backward)" if graphs is not None else "eager launches"
@@ -571,6 +579,8 @@ def run_b200(a):
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
             "gpu_launches": launches_per_step * a.steps, "device_status": device_status,
         }
+        if ref_cuda_res is not None:
+            line["reference_cuda"] = ref_cuda_res
         if shard_check is not None:
             line["shard_check"] = shard_check
         if long_seq is not None:
@@ -578,6 +588,54 @@ def run_b200(a):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def reference_cuda_leg(a, torch, pkg, d, u, N, ours):
+    """The reference's own CUDA kernels (rwkv_kernels.cu compiled unchanged for sm_100a into oracle/_ref/, see
+    oracle/build_ref_cuda.py) on the same inputs on this GPU: a reported baseline beside the host-core one."""
+    from oracle import ref_cuda
+    if not ref_cuda.available():
+        return {"unavailable": "oracle/_ref/libref_wkv6_cuda.so has not been built (it is compiled where the reference tree is at hand)"}
+    B, T, C = d["r"].shape
+    if N != ref_cuda.HEAD_SIZE or T > ref_cuda.MAX_T or T < 3 or a.dtype != "bf16":
+        return {"unavailable": f"the reference kernels are compiled for head size {ref_cuda.HEAD_SIZE}, T <= {ref_cuda.MAX_T}"}
+    ub = u.to(d["r"].dtype)                               # the reference takes u in the dtype of r, k, v, w
+    y = torch.empty_like(d["r"])
+    g = [torch.empty_like(d["r"]) for _ in range(4)]
+    gu = torch.empty((B, C), dtype=d["r"].dtype, device=d["r"].device)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        ref_cuda.forward(d["r"], d["k"], d["v"], d["w"], ub, y, st)
+        ref_cuda.backward(d["r"], d["k"], d["v"], d["w"], ub, d["gy"], *g, gu, st)
+
+    step()
+    torch.cuda.synchronize()
+    if ref_cuda.lib().ref_wkv6_last_cuda_error() != 0:
+        return {"unavailable": "the reference kernels reported a CUDA error on their first launch"}
+    for _ in range(2):
+        step()
+    steps = 5
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    e[0].record()
+    for _ in range(steps):
+        ref_cuda.forward(d["r"], d["k"], d["v"], d["w"], ub, y, st)
+    e[1].record()
+    for _ in range(steps):
+        ref_cuda.backward(d["r"], d["k"], d["v"], d["w"], ub, d["gy"], *g, gu, st)
+    e[2].record()
+    torch.cuda.synchronize()
+    fwd_ms, bwd_ms = e[0].elapsed_time(e[1]) / steps, e[1].elapsed_time(e[2]) / steps
+    yo, go = ours
+    agree = max([_scaled_err(y, yo)] + [_scaled_err(x, x0) for x, x0 in zip(g, go[:4])]
+                + [_scaled_err(gu.view(go[4].shape), go[4])])
+    peak, _ = measured_peak()
+    ms = fwd_ms + bwd_ms
+    return {"value": B * T / (ms * 1e-3) / 1e6, "unit": UNIT, "ms_per_step": ms, "forward_ms": fwd_ms, "backward_ms": bwd_ms,
+            "steps": steps, "warmup": 3, "roofline_step_frac": 28.0 * B * T * C / (ms * 1e-3) / 1e9 / peak,
+            "kernels": "rwkv_kernel/jax_kernel/rwkv_kernels.cu of the reference, unchanged, nvcc -O3 -DNDEBUG for sm_100a, "
+                       "_N_=64 _T_=4096; forward 1 launch, backward 4 launches",
+            "max_scaled_difference_to_this_library": agree}
 
 
 def long_sequence_leg(a, torch, dist, pkg, seg, dev, rank, world, N):

@@ -284,12 +284,25 @@ WKV6_API int wkv6_copy_2d_async(void *dst, size_t dst_pitch, const void *src, si
  * they throw std::runtime_error on failure as the reference does for a bad descriptor.  The functions below are
  * the same handlers with an error code instead of an exception, the descriptor packer that replaces
  * gpu_ops.create_rwkv_descriptor (rwkv_kernel/jax_kernel/gpu_ops.cpp:33-36; returns the blob size, 28), and the
- * handler addresses (0 forward, 1 backward, 2 forward_with_state) for "xla._CUSTOM_CALL_TARGET" capsules
- * (replaces gpu_ops.get_rwkv_registrations, gpu_ops.cpp:20-29).
+ * handler addresses (0 forward, 1 backward, 2 forward_with_state, 3 forward_ckpt, 4 backward_ws) for
+ * "xla._CUSTOM_CALL_TARGET" capsules (replaces gpu_ops.get_rwkv_registrations, gpu_ops.cpp:20-29).
+ *
+ * wkv_backward keeps the reference's eleven buffers (rwkv_kernels.cu:493-508) and so has no scratch: it runs the
+ * sequential kernels on the library's built-in array, in slices when the problem is larger than the array.  The two
+ * extended handlers reach the chunked tensor-core kernels for any size by letting the lowering declare two more
+ * buffers (the legacy ABI's way to get a workspace: an extra result):
+ *   wkv6_xla_forward_ckpt   [r, k, v, w, u, y, ckpt]                            ckpt = extra result, residual of the vjp
+ *   wkv6_xla_backward_ws    [r, k, v, w, u, gy, ckpt, gr, gk, gv, gw, gu, ws]   ws = extra result, scratch
+ * wkv6_xla_buffer_bytes(descriptor, which) gives the least size of ckpt (which = 0) and ws (which = 1); the shapes
+ * [B, H, ceil(T/64), 4096] bf16 and [B, H, 64] int32 always suffice for bf16 inputs with head size 64 and split with
+ * the (batch, head) pairs under a partitioning rule.
  */
 WKV6_API int wkv6_xla_forward(void *stream, void **buffers, const char *opaque, size_t opaque_len);
 WKV6_API int wkv6_xla_backward(void *stream, void **buffers, const char *opaque, size_t opaque_len);
 WKV6_API int wkv6_xla_forward_with_state(void *stream, void **buffers, const char *opaque, size_t opaque_len);
+WKV6_API int wkv6_xla_forward_ckpt(void *stream, void **buffers, const char *opaque, size_t opaque_len);
+WKV6_API int wkv6_xla_backward_ws(void *stream, void **buffers, const char *opaque, size_t opaque_len);
+WKV6_API size_t wkv6_xla_buffer_bytes(const char *opaque, size_t opaque_len, int which);
 WKV6_API int wkv6_xla_descriptor(int B, int T, int C, int H, int S, int x_type, int y_type, char *out, size_t out_len);
 WKV6_API void *wkv6_xla_target(int which);
 

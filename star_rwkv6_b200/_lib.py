@@ -24,7 +24,8 @@ SYMBOLS = (
     "wkv6_decode_sigmoid_mul_add", "wkv6_softmax_xent_bf16", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
     "wkv6_groupnorm_gate_forward", "wkv6_groupnorm_gate_backward", "wkv6_groupnorm_gate_workspace_bytes",
     "wkv6_shift_mix_forward", "wkv6_shift_mix_backward", "wkv6_shift_mix_workspace_bytes", "wkv6_copy_2d_async",
-    "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_descriptor", "wkv6_xla_target",
+    "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_forward_ckpt", "wkv6_xla_backward_ws",
+    "wkv6_xla_buffer_bytes", "wkv6_xla_descriptor", "wkv6_xla_target",
 )
 
 
@@ -108,7 +109,10 @@ def _load():
     lib.wkv6_shift_mix_workspace_bytes.argtypes = [i32] * 4
     lib.wkv6_copy_2d_async.restype = ctypes.c_int
     lib.wkv6_copy_2d_async.argtypes = [vp, sz, vp, sz, sz, sz, i32, vp]
-    for name in ("wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state"):
+    lib.wkv6_xla_buffer_bytes.restype = sz
+    lib.wkv6_xla_buffer_bytes.argtypes = [ctypes.c_char_p, sz, ctypes.c_int]
+    for name in ("wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_forward_ckpt",
+                 "wkv6_xla_backward_ws"):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [vp, ctypes.POINTER(vp), ctypes.c_char_p, sz]

@@ -25,6 +25,17 @@ def sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
+def xla_ffi_include_dir():
+    """Directory of jaxlib's xla/ffi/api/ffi.h, or None: the typed-FFI handlers (csrc/wkv6_xla_ffi.cc) are compiled
+    into the library only where JAX is installed."""
+    try:
+        import jax.ffi
+        inc = jax.ffi.include_dir()
+    except Exception:
+        return None
+    return inc if os.path.exists(os.path.join(inc, "xla", "ffi", "api", "ffi.h")) else None
+
+
 def _stale() -> bool:
     if not os.path.exists(LIB):
         return True
@@ -42,6 +53,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in sources():
         obj = os.path.splitext(src)[0] + ".o"
         cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+        procs.append((cmd, subprocess.Popen(cmd)))
+        objs.append(obj)
+    inc = xla_ffi_include_dir()
+    if inc is not None:   # exported with default visibility: the handler symbols are what jax.ffi.pycapsule looks up
+        src, obj = os.path.join(CSRC, "wkv6_xla_ffi.cc"), os.path.join(CSRC, "wkv6_xla_ffi.o")
+        flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
+        cmd = [nvcc, "-x", "cu"] + flags + ["-I", inc, "-c", src, "-o", obj]
         procs.append((cmd, subprocess.Popen(cmd)))
         objs.append(obj)
     for cmd, pr in procs:

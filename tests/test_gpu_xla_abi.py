@@ -74,3 +74,59 @@ def test_forward_with_state_buffers():
     torch.cuda.synchronize()
     yo, so = c_oracle.fwd(d["r"], d["k"], d["v"], d["w"], d["u"], N)
     assert scaled_err(np_(y), yo) <= TOL_F32 and scaled_err(np_(ys), so) <= TOL_F32
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,T,H", [(3, 4096, 16), (1, 8192, 24)])
+def test_legacy_backward_beyond_the_built_in_scratch(B, T, H):
+    """Eleven buffers, bf16, more (token, channel) pairs than the built-in scratch holds: the handler cuts the problem
+    into whole rows (first case: 2 + 1) or head groups of a row (second case: 16 + 8 heads); (batch, head) sequences are
+    independent, so the result equals the one-call backward of the same kernels bit for bit."""
+    import star_rwkv6_b200 as pkg
+    from star_rwkv6_b200 import _lib as L
+    N = 64
+    assert B * T * H * N * 4 > L.lib.wkv6_static_scratch_bytes()
+    g = torch.Generator(device="cuda").manual_seed(B + T)
+    mk = lambda s: (torch.randn(B, T, H * N, generator=g, device="cuda") * s).to(torch.bfloat16)
+    t = dict(r=mk(0.125), k=mk(0.125), v=mk(0.125), gy=mk(1.0),
+             w=(torch.rand(B, T, H * N, generator=g, device="cuda") * 7 - 6).to(torch.bfloat16))
+    u = (torch.randn(H, N, generator=g, device="cuda") * 0.1).to(torch.bfloat16)
+    outs = [torch.empty_like(t["r"]) for _ in range(4)]
+    gu = torch.empty((B, H * N), dtype=torch.bfloat16, device="cuda")
+    desc = L.xla_descriptor(B, T, H * N, H, False, 0, 0)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = L.lib.wkv6_xla_backward(st, _buffers([t["r"], t["k"], t["v"], t["w"], u, t["gy"], *outs, gu]), desc, len(desc))
+    assert rc == 0, L.lib.wkv6_last_error()
+    want = pkg.backward_raw(t["r"], t["k"], t["v"], t["w"], u, t["gy"], N, variant=pkg.VARIANT_SEQ)
+    torch.cuda.synchronize()
+    for a, b in zip(outs, want[:4]):
+        assert torch.equal(a, b)
+    assert torch.equal(gu.view(B, H, N), want[4].to(torch.bfloat16))
+
+
+@pytest.mark.gpu
+def test_extended_buffer_orders_at_the_headline_size():
+    """wkv_forward_ckpt / wkv_backward_ws at B8 T4096 H32 bf16 (the chunked kernels behind the XLA surface): y and the
+    five gradients against the oracle on sampled (batch, head) sequences."""
+    from star_rwkv6_b200 import _lib as L
+    from test_gpu_fullsize import check_sampled, gen
+    B, T, H, N = 8, 4096, 32, 64
+    d = gen(B, T, H, seed=2)
+    u = d["u"].to(torch.bfloat16)                      # the legacy descriptor gives u the dtype of r, k, v, w
+    desc = L.xla_descriptor(B, T, H * N, H, False, 0, 0)
+    ck_bytes, ws_bytes = (L.lib.wkv6_xla_buffer_bytes(desc, len(desc), i) for i in (0, 1))
+    assert ck_bytes == B * H * (T // 64) * 4096 * 2 and 16 <= ws_bytes <= B * H * 64 * 4
+    y = torch.empty_like(d["r"])
+    ckpt = torch.empty((B, H, T // 64, 4096), dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty((B, H, 64), dtype=torch.int32, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = L.lib.wkv6_xla_forward_ckpt(st, _buffers([d["r"], d["k"], d["v"], d["w"], u, y, ckpt]), desc, len(desc))
+    assert rc == 0, L.lib.wkv6_last_error()
+    g = [torch.empty_like(d["r"]) for _ in range(4)]
+    gu = torch.empty((B, H, N), dtype=torch.bfloat16, device="cuda")
+    rc = L.lib.wkv6_xla_backward_ws(st, _buffers([d["r"], d["k"], d["v"], d["w"], u, d["gy"], ckpt, *g, gu, ws]), desc, len(desc))
+    assert rc == 0, L.lib.wkv6_last_error()
+    torch.cuda.synchronize()
+    assert L.lib.wkv6_device_status() == 0
+    d2 = dict(d, u=u.float())
+    check_sampled(d2, [(1, 3), (6, 30)], y, (*g, gu.float()))
