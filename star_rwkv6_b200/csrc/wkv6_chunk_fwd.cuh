@@ -91,11 +91,10 @@ struct ChunkFwdArgs {
     __nv_bfloat16 *ckpt;  // optional [B*H][T/64][64*64] bf16 chunk-start states in operand (swizzled) layout
     int B, T, H;
     bool write_y;         // false: only states / checkpoints are produced
-    // Segment summaries (see wkv6_segment_summary): walk the chunks from last to first and accumulate
-    // sum_t (x1_t e^{c_{t-1}}) (x) x2_t instead of sum_t (x1_t e^{c_end - c_t}) (x) x2_t, i.e. the reverse state of the
-    // backward when x1 = r and x2 = gy are passed in the k and v slots.
+    // Used by the summary kernel only (wkv6_chunk_summary.cuh): walk the chunks from last to first and accumulate the
+    // reverse state of the backward (x1 = r, x2 = gy); and where to leave log2 of the total decay per key channel.
     bool reverse_state;
-    float *dec_out;       // optional [B*H][64]: log2 of the total decay of the sequence per key channel
+    float *dec_out;       // optional [B*H][64]
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -245,7 +244,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     const int skip_chunk = *reinterpret_cast<volatile int *>(&g_skip_load_chunk);  // test hook, -1 in normal use
     auto issue_loads = [&](int ic2) {  // every thread calls it; the four loading threads act
         if (load_slot < 0 || ic2 == skip_chunk) return;
-        const int c = a.reverse_state ? nchunks - 1 - ic2 : ic2;
+        const int c = ic2;
         const int st = ic2 & 1;
         uint8_t *dst = smem + st * SM::kStage + load_slot * kTile;
         const CUtensorMap *tm = load_slot == 0 ? &tm_r : load_slot == 1 ? &tm_k : load_slot == 2 ? &tm_v : &tm_w;
@@ -275,44 +274,43 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
 
     int err = 0;
     int loads_issued = (nchunks > 1) ? 2 : 1, loads_consumed = 0;  // chunks whose loads were issued / waited for
-    float2 dsum = make_float2(0.f, 0.f);  // warp 0: log2 of the decay accumulated over all chunks, channels 2*lane, +1
-    for (int ic = 0; ic < nchunks; ++ic) {
-        const int c = a.reverse_state ? nchunks - 1 - ic : ic;  // chunk processed in this iteration
+    // Pass 1 of a chunk: per-step log2 decays of this thread's 8 tokens x 2 channels and their running sums from the
+    // first of them, block partial sums to shared memory.  It needs only the w tile, so it runs one chunk ahead, inside
+    // the window in which the second MMA group of the chunk before executes.
+    // Row t = 16*w4 + 8*half + tt has swizzle phase tt, so one per-thread base pointer plus a per-tt XOR term
+    // addresses every tile (tile offsets are compile-time constants relative to the stage base).
+    const uint32_t lane_chunk = (uint32_t)(lane >> 2);
+    const uint32_t tofs = (uint32_t)((16 * w4 + 8 * half) * 128 + ((lane & 3) << 2));
+    float2 x[8];
+    auto pass1 = [&](int ic1) {
+        const uint8_t *wt = smem + (ic1 & 1) * SM::kStage + 3 * kTile + tofs;
+        const bool full_chunk = (ic1 + 1) * kChunk <= a.T;
+        float2 cs = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            const float2 w2 = ld_bf2(wt + tt * 128 + ((lane_chunk ^ tt) << 4));
+            const float2 e2 = mul2(w2, make_float2(kLog2e, kLog2e));
+            float2 l2 = mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
+            l2.x = fmaxf(l2.x, kMinLogDecay2);
+            l2.y = fmaxf(l2.y, kMinLogDecay2);
+            if (!full_chunk && ic1 * kChunk + 16 * w4 + 8 * half + tt >= a.T) l2 = make_float2(0.f, 0.f);
+            cs = add2(cs, l2);
+            x[tt] = cs;
+        }
+        *reinterpret_cast<float2 *>(&(half ? sTail : sHead)[w4 * 64 + 2 * lane]) = cs;
+    };
+    if (!cta_wait(&bar_full[0], 0, warp)) err = 1;
+    if (err == 0) ++loads_consumed;
+    pass1(0);
+    if (!__syncthreads_and(err == 0)) err = err ? err : 10;
+
+    for (int ic = 0; ic < nchunks && err == 0; ++ic) {
+        const int c = ic;  // chunk processed in this iteration
         const int st = ic & 1;
         uint8_t *sR = smem + st * SM::kStage;  // this stage: r, k, v, w tiles at +0, +kTile, +2 kTile, +3 kTile
         const uint64_t so = (uint64_t)(st * (SM::kStage >> 4));
-        WKV6_TSTAMP(ic, 0);
-        if (!cta_wait(&bar_full[st], (ic >> 1) & 1, warp)) err = 1;
-        if (err == 0) ++loads_consumed;
-        WKV6_TSTAMP(ic, 1);
-
-        // ---- pass 1: per-step log2 decays of this thread's 8 tokens x 2 channels, running sums from the first of them.
-        // Row t = 16*w4 + 8*half + tt has swizzle phase tt, so one per-thread base pointer plus a per-tt XOR term
-        // addresses every tile (tile offsets are compile-time constants relative to the stage base).
-        uint8_t *const tbase = sR + (16 * w4 + 8 * half) * 128 + ((lane & 3) << 2);
-        const uint32_t lane_chunk = (uint32_t)(lane >> 2);
-        const bool full_chunk = (c + 1) * kChunk <= a.T;
+        uint8_t *const tbase = sR + tofs;
         bool wide;  // single reference point for this chunk (the same value in every warp)
-        float2 x[8];
-        {
-            float2 cs = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int tt = 0; tt < 8; ++tt) {
-                const uint8_t *pt = tbase + tt * 128 + ((lane_chunk ^ tt) << 4);
-                const float2 w2 = ld_bf2(pt + 3 * kTile);
-                const float2 e2 = mul2(w2, make_float2(kLog2e, kLog2e));
-                float2 l2 = mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
-                l2.x = fmaxf(l2.x, kMinLogDecay2);
-                l2.y = fmaxf(l2.y, kMinLogDecay2);
-                if (!full_chunk && c * kChunk + 16 * w4 + 8 * half + tt >= a.T) l2 = make_float2(0.f, 0.f);
-                cs = add2(cs, l2);
-                x[tt] = cs;
-            }
-            *reinterpret_cast<float2 *>(&(half ? sTail : sHead)[w4 * 64 + 2 * lane]) = cs;
-        }
-        // the previous chunk's y tile and checkpoint copies must have left shared memory before it is rewritten
-        if (copy_thread) bulk_wait_read<0>();
-        if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
         WKV6_TSTAMP(ic, 2);
 
         // ---- pass 2: scaled operands.  The block reference is the boundary between the two token halves, so the
@@ -357,10 +355,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                     }
                 }
             }
-            if (warp == 0) {
-                *reinterpret_cast<float2 *>(&sDtot[2 * lane]) = make_float2(ex2f(all.x), ex2f(all.y));
-                dsum = add2(dsum, all);
-            }
+            if (warp == 0) *reinterpret_cast<float2 *>(&sDtot[2 * lane]) = make_float2(ex2f(all.x), ex2f(all.y));
             const float2 fK = make_float2(ex2f(all.x - ref.x), ex2f(all.y - ref.y));  // decay from the reference point to the chunk end
             if (warp == 4) *reinterpret_cast<float2 *>(&sFK[2 * lane]) = wide ? fK : make_float2(1.f, 1.f);
             const int kdo = (int)(sKD - sR), kho = (int)(sKH - sR);  // uniform offsets of the copy tiles from this stage
@@ -454,6 +449,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
                 }
             }
         }
+        // the previous chunk's y tile and checkpoint copies must have left shared memory before the epilogues rewrite them
+        if (copy_thread) bulk_wait_read<0>();
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
@@ -474,8 +471,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         } else if (tid == 64) {
             tc_fence_after_sync();
 #pragma unroll
-            // state increment = k~^T v with its rows scaled afterwards, or k^^T v (reverse-state mode: r^^T x2, r^ sits in the w tile)
-            const uint64_t dInc = a.reverse_state ? dW + so : (wide ? dK + so : dKH);
+            // state increment = k~^T v with its rows scaled afterwards, or k^^T v
+            const uint64_t dInc = wide ? dK + so : dKH;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) umma_ss(tmS, dInc + 128 * kk, dV + so + 128 * kk, idMM, kk > 0);
 #pragma unroll
@@ -491,7 +488,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         // ---- epilogue of the intra-chunk matrix: pick, mask, round, store as the A operand of A v.
         // This warp covers column blocks J = 2*half and 2*half + 1 of row block I = w4.
         const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
-        const float g0 = a.reverse_state ? 1.f : sFK[ta], g1 = a.reverse_state ? 1.f : sFK[ta + 8];
+        const float g0 = sFK[ta], g1 = sFK[ta + 8];
         {
             const int I = w4;
 #pragma unroll
@@ -566,13 +563,18 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         } else if (copy_thread) {
             // the state entering the next chunk is complete in shared memory: checkpoint it for the backward.
             // Its read is drained (bulk_wait_read) before the next chunk's first barrier, ahead of the rewrite.
-            if (a.ckpt != nullptr && !a.reverse_state && c + 1 < nchunks) {
+            if (a.ckpt != nullptr && c + 1 < nchunks) {
                 bulk_store(a.ckpt + ((size_t)blockIdx.x * nchunks + c + 1) * 4096, sSB, kTile);
                 bulk_commit();
             }
         }
         WKV6_TSTAMP(ic, 7);
-        if (!cta_wait(bar_mma2, ic & 1, warp)) err = 3;
+        if (ic + 1 < nchunks) {  // the next chunk's decays, while the tensor core works
+            if (!cta_wait(&bar_full[st ^ 1], ((ic + 1) >> 1) & 1, warp)) err = 1;
+            if (err == 0) ++loads_consumed;
+            pass1(ic + 1);
+        }
+        if (!cta_wait(bar_mma2, ic & 1, warp)) err = err ? err : 3;
         tc_fence_after_sync();
         WKV6_TSTAMP(ic, 8);
 
@@ -610,8 +612,6 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         if (err != 0) atomicExch(&g_chunk_status, err);
         bulk_wait<0>();
     }
-    if (err == 0 && a.dec_out != nullptr && warp == 0)
-        *reinterpret_cast<float2 *>(a.dec_out + (size_t)blockIdx.x * 64 + 2 * lane) = dsum;
     if (err == 0 && a.s_out != nullptr) {
         const size_t so2 = (size_t)blockIdx.x * 4096;
 #pragma unroll
