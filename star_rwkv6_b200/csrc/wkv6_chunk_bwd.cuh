@@ -138,49 +138,6 @@ __device__ __forceinline__ void scan_suffix16(float &a, float &b, int r0, int la
     a += __shfl_sync(0xffffffffu, b, lane & 3);
 }
 
-// The same scans for eight value pairs at once: every step issues its sixteen shuffles back to back, so their
-// latencies overlap (one scan after the other leaves each shuffle waiting for the one before it).
-__device__ __forceinline__ void scan_prefix16_x8(float (&a)[8], float (&b)[8], int r0, int lane) {
-#pragma unroll
-    for (int d = 1; d < 8; d <<= 1) {
-        float ta[8], tb[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            ta[i] = __shfl_up_sync(0xffffffffu, a[i], 4 * d);
-            tb[i] = __shfl_up_sync(0xffffffffu, b[i], 4 * d);
-        }
-        if (r0 >= d) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { a[i] += ta[i]; b[i] += tb[i]; }
-        }
-    }
-    float t[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) t[i] = __shfl_sync(0xffffffffu, a[i], 28 + (lane & 3));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) b[i] += t[i];
-}
-__device__ __forceinline__ void scan_suffix16_x8(float (&a)[8], float (&b)[8], int r0, int lane) {
-#pragma unroll
-    for (int d = 1; d < 8; d <<= 1) {
-        float ta[8], tb[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            ta[i] = __shfl_down_sync(0xffffffffu, a[i], 4 * d);
-            tb[i] = __shfl_down_sync(0xffffffffu, b[i], 4 * d);
-        }
-        if (r0 + d < 8) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { a[i] += ta[i]; b[i] += tb[i]; }
-        }
-    }
-    float t[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) t[i] = __shfl_sync(0xffffffffu, b[i], lane & 3);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) a[i] += t[i];
-}
-
 __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant__ CUtensorMap tm_r,
                                                            const __grid_constant__ CUtensorMap tm_k,
                                                            const __grid_constant__ CUtensorMap tm_v,

@@ -233,10 +233,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
                     const float2 e2 = mul2(ld_bf2(sW + FO(nn, hrow)), make_float2(kLog2e, kLog2e));
-                    float2 l2 = KO(1) ? make_float2(-0.5f, -0.5f) : mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
+                    float2 l2 = mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
                     l2.x = fmaxf(l2.x, kMinLogDecay2);
                     l2.y = fmaxf(l2.y, kMinLogDecay2);
-                    if (!KO(1) && !full_chunk && c * kChunk + ta + 8 * hrow >= a.T) l2 = make_float2(0.f, 0.f);
+                    if (!full_chunk && c * kChunk + ta + 8 * hrow >= a.T) l2 = make_float2(0.f, 0.f);
                     lw[4 * nn + 2 * hrow] = l2.x;
                     lw[4 * nn + 2 * hrow + 1] = l2.y;
                     { const __nv_bfloat162 lb = to_bf2(l2); lwst[2 * nn + hrow] = *reinterpret_cast<const uint32_t *>(&lb); }
@@ -244,28 +244,15 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             }
             tmem_st_16x256b_x2(tmStash, lwst);
         }
-        if (EXP(0)) {
-            float pa[8], pb[8];
-#pragma unroll
-            for (int nn = 0; nn < 4; ++nn)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) { pa[2 * nn + e] = lw[4 * nn + e]; pb[2 * nn + e] = lw[4 * nn + 2 + e]; }
-            scan_prefix16_x8(pa, pb, r0, lane);
-#pragma unroll
-            for (int nn = 0; nn < 4; ++nn)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) { cs[4 * nn + e] = pa[2 * nn + e]; cs[4 * nn + 2 + e] = pb[2 * nn + e]; }
-        } else {
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 float pa = lw[4 * nn + e], pb = lw[4 * nn + 2 + e];
-                if (!KO(0)) scan_prefix16(pa, pb, r0, lane);
+                scan_prefix16(pa, pb, r0, lane);
                 cs[4 * nn + e] = pa;
                 cs[4 * nn + 2 + e] = pb;
             }
-        }
         if (r0 == 7) {
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
@@ -330,27 +317,23 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                     const __nv_bfloat162 kb = *reinterpret_cast<const __nv_bfloat162 *>(sK + off);
                     const float2 ea = make_float2(cs[e0] - lw[e0] - of.x, cs[e0 + 1] - lw[e0 + 1] - of.y);
                     const float2 eb = make_float2(of.x - cs[e0], of.y - cs[e0 + 1]);
-                    const __nv_bfloat162 er = KO(3) ? to_bf2(ea) : to_bf2(make_float2(ex2f(ea.x), ex2f(ea.y)));
-                    const __nv_bfloat162 ek = KO(3) ? to_bf2(eb) : to_bf2(make_float2(ex2f(eb.x), ex2f(eb.y)));
+                    const __nv_bfloat162 er = to_bf2(make_float2(ex2f(ea.x), ex2f(ea.y)));
+                    const __nv_bfloat162 ek = to_bf2(make_float2(ex2f(eb.x), ex2f(eb.y)));
                     ekb[2 * nn + hrow] = ek;
-                    if (!KO(4)) {
                     const float2 rk = mul2(__bfloat1622float2(rb), __bfloat1622float2(kb));
                     const float bon = fmaf(rk.x, uc.x, rk.y * uc.y);
                     if (hrow == 0) bon_a += bon; else bon_b += bon;
-                    }
                     const __nv_bfloat162 rt = __hmul2(rb, er), kt = __hmul2(kb, ek);
                     *reinterpret_cast<__nv_bfloat162 *>(sET + off) = er;
                     *reinterpret_cast<__nv_bfloat162 *>(sRT + off) = rt;
-                    if (!KO(5)) *reinterpret_cast<__nv_bfloat162 *>(sW + off) = __hmul2(rt, frb);
+                    *reinterpret_cast<__nv_bfloat162 *>(sW + off) = __hmul2(rt, frb);
                     *reinterpret_cast<__nv_bfloat162 *>(sKT + off) = kt;
-                    if (!KO(5)) *reinterpret_cast<__nv_bfloat162 *>(sKH + off) = __hmul2(kt, fkb);
+                    *reinterpret_cast<__nv_bfloat162 *>(sKH + off) = __hmul2(kt, fkb);
                 }
             }
-            if (!KO(4)) {
             bon_a += __shfl_xor_sync(0xffffffffu, bon_a, 1); bon_a += __shfl_xor_sync(0xffffffffu, bon_a, 2);
             bon_b += __shfl_xor_sync(0xffffffffu, bon_b, 1); bon_b += __shfl_xor_sync(0xffffffffu, bon_b, 2);
             if (q == 0) { sBonus[half * 64 + ta] = bon_a; sBonus[half * 64 + ta + 8] = bon_b; }
-            }
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
@@ -427,7 +410,6 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                 *reinterpret_cast<uint32_t *>(sP + FO(nn, 1)) = pack_bf2(x10, x11);
             }
             // A: this warp covers column blocks J = 2*half, 2*half+1 of row block I = w4
-            if (!KO(7))
 #pragma unroll
             for (int jj = 0; jj < 2; ++jj) {
                 const int J = 2 * half + jj, I = w4;
@@ -460,7 +442,6 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             float AB[16];
             tmem_ld_16x256b_x4(tmABp, AB);
             float za = 0.f, zb = 0.f;
-            if (!KO(8)) {
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 const float2 sa = ld_bf2(sS + FO(nn, 0)), sb = ld_bf2(sS + FO(nn, 1));
@@ -470,8 +451,6 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             za += __shfl_xor_sync(0xffffffffu, za, 1); za += __shfl_xor_sync(0xffffffffu, za, 2);
             zb += __shfl_xor_sync(0xffffffffu, zb, 1); zb += __shfl_xor_sync(0xffffffffu, zb, 2);
             if (q == 0) { sT1[half * 64 + ta] = za; sT1[half * 64 + ta + 8] = zb; }
-            }
-            if (!KO(9)) {
             tmem_ld_16x256b_x4(tmAN + lo + cb, f);  // rows are key channels here
             const float d0 = sDtot[ta], d1 = sDtot[ta + 8];
 #pragma unroll
@@ -485,7 +464,6 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             }
             tmem_st_16x256b_x4(tmABp, AB);
             tmem_wait_st();
-            }
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
@@ -522,11 +500,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         {
             const float vga = sVG[ta], vgb = sVG[ta + 8];
             float gu8[8], bs8[8];  // per-channel sums over this thread's two tokens: r k vg (for gu) and b (for gw)
-            float qa[8], qb[8];    // q of rows ta / ta + 8 (batched suffix scans)
 #pragma unroll
             for (int e = 0; e < 8; ++e) gu8[e] = bs8[e] = 0.f;
-            if (KO(10)) { for (int e = 0; e < 16; ++e) loc[e] = 0.f; }
-            else
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 const int col = 8 * (n0 + nn) + 2 * q;
@@ -561,8 +536,6 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                     *reinterpret_cast<__nv_bfloat162 *>(sP + off) = to_bf2(gr);
                     *reinterpret_cast<__nv_bfloat162 *>(sAM + off) = to_bf2(gk);
                     // gw pieces: a = r~ GR1 + r^ GR2 = r~ (GR1 + fR GR2) (fR is a power of two), z = k~ GK1, b = k^ GK2
-                    if (KO(11)) { qv[2 * hrow] = qv[2 * hrow + 1] = 0.f; loc[4 * nn + 2 * hrow] = loc[4 * nn + 2 * hrow + 1] = 0.f; }
-                    else {
                     const float2 av = mul2(rt, MR);
                     const float2 bv = mul2(mul2(kt, fk), H2);
                     const float2 zbv = fma2(kt, H1, bv);
@@ -571,40 +544,21 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                     loc[4 * nn + 2 * hrow] = -av.x;      // becomes  suffix_incl(q) - q - (z + b) = suffix_incl(q) - a
                     loc[4 * nn + 2 * hrow + 1] = -av.y;
                     bs8[2 * nn] += bv.x; bs8[2 * nn + 1] += bv.y;
-                    }
-                    if (!KO(13)) {
                     const float2 rkv = mul2(mul2(r2, k2), make_float2(vg, vg));
                     gu8[2 * nn] += rkv.x;
                     gu8[2 * nn + 1] += rkv.y;
-                    }
                 }
                 // sums over later tokens of the block by lane scans; block totals go through shared memory
-                if (EXP(1)) {
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) { qa[2 * nn + e] = qv[e]; qb[2 * nn + e] = qv[2 + e]; }
-                } else {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     float pa = qv[e], pb = qv[2 + e];
-                    if (!KO(12) && !KO(11)) scan_suffix16(pa, pb, r0, lane);
+                    scan_suffix16(pa, pb, r0, lane);
                     loc[4 * nn + e] += pa;
                     loc[4 * nn + 2 + e] += pb;
                     if (r0 == 0) sXtot[w4 * 64 + col + e] = pa;
                 }
-                }
             }
-            if (EXP(1) && !KO(10)) {
-                scan_suffix16_x8(qa, qb, r0, lane);
-#pragma unroll
-                for (int nn = 0; nn < 4; ++nn)
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        loc[4 * nn + e] += qa[2 * nn + e];
-                        loc[4 * nn + 2 + e] += qb[2 * nn + e];
-                        if (r0 == 0) sXtot[w4 * 64 + 8 * (n0 + nn) + 2 * q + e] = qa[2 * nn + e];
-                    }
-            }
-            if (!KO(11)) {   // block totals of b: 8 channel sums over the 8 lanes that share q, in 7 shuffles; lane r0 ends with channel
+            {   // block totals of b: 8 channel sums over the 8 lanes that share q, in 7 shuffles; lane r0 ends with channel
                 // value index e = 4*bit4 + 2*bit3 + bit2 of its lane number
                 const bool u4 = (lane & 16) != 0, u3 = (lane & 8) != 0, u2 = (lane & 4) != 0;
 #pragma unroll
@@ -624,7 +578,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                 const int e = (u4 ? 4 : 0) + (u3 ? 2 : 0) + (u2 ? 1 : 0);  // value index: channel 8 (n0 + e/2) + 2 q + (e & 1)
                 sBtot[w4 * 64 + 8 * (n0 + (e >> 1)) + 2 * q + (e & 1)] = bs8[0];
             }
-            if (!KO(13)) {   // running sums of gu live in tensor memory between chunks
+            {   // running sums of gu live in tensor memory between chunks
                 float acc[8];
                 tmem_ld_16x256b_x2(tmGUp, acc);
 #pragma unroll
@@ -632,10 +586,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                 tmem_st_16x256b_x2(tmGUp, acc);
             }
             float gv16[16];
-            if (!KO(15)) {
             tmem_ld_16x256b_x4(tmGV + lo + cb, gv16);
-            }
-            if (!KO(15))
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {  // the k~ tile is free: its last reader was the second MMA group
                 *reinterpret_cast<uint32_t *>(sKT + FO(nn, 0)) = pack_bf2(gv16[4 * nn], gv16[4 * nn + 1]);
@@ -650,11 +601,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         if (copy_thread && c > 0 && err == 0) issue_rk(c - 1);
         // G_t = e^{c_63} <S_in, Abar> + sum_all b + sum_{later blocks} q + (suffix_incl(q) - a)_t ;  gw = -exp(w) G
         uint32_t lwst2[8];
-        if (!KO(14)) {
         tmem_ld_16x256b_x2(tmStash, lwst2);
         tmem_wait_ld();
-        }
-        if (!KO(14))
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn) {
             const int col = 8 * (n0 + nn) + 2 * q;

@@ -58,15 +58,6 @@ __device__ long long g_chunk_timing[64][16][8];
 #define WKV6_TSTAMP(iter, k) do { } while (0)
 #endif
 
-#ifndef WKV6_KO
-#define WKV6_KO 0
-#endif
-#define KO(n) (((WKV6_KO) >> (n)) & 1)
-#ifndef WKV6_EXP
-#define WKV6_EXP 0
-#endif
-#define EXP(n) (((WKV6_EXP) >> (n)) & 1)
-
 struct ChunkFwdSmem {
     static constexpr int kStage = 4 * kTile;                 // r, k, v, w
     static constexpr int oStage0 = 0;
