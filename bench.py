@@ -672,11 +672,34 @@ def long_sequence_leg(a, torch, dist, pkg, seg, dev, rank, world, N):
         step()
     dist.barrier()
     torch.cuda.synchronize()
+    # one CUDA graph per step, the NCCL all-gathers of the summaries inside it (eager launches when capture is refused)
+    run, launch = step, "eager launches, NCCL all-gather of the summaries inside every step"
+    if not a.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    step()
+            torch.cuda.current_stream().wait_stream(side)
+            graph.replay()
+            torch.cuda.synchronize()
+            run, launch = graph.replay, "one CUDA graph replay per step, the NCCL all-gathers of the summaries captured in it"
+        except Exception as exc:  # noqa: BLE001
+            launch += f" (graph capture refused: {type(exc).__name__})"
+            torch.cuda.synchronize()
+    ok = torch.tensor([1.0 if run is not step else 0.0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)      # every rank must take the same path: collectives pair up across ranks
+    if ok.item() == 0.0:
+        run = step
+    dist.barrier()
+    torch.cuda.synchronize()
     steps = 10
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        step()
+        run()
     e1.record()
     dist.barrier()
     torch.cuda.synchronize()
@@ -687,7 +710,7 @@ def long_sequence_leg(a, torch, dist, pkg, seg, dev, rank, world, N):
     return {"workload": f"wkv6 fwd+bwd B{B} T{T} H{H} N{N} bf16, T sharded over {world} ranks, {G} segments per rank",
             "ms_per_step": ms, "value": B * T / (ms * 1e-3) / 1e6, "unit": UNIT, "steps": steps, "warmup": 3,
             "roofline_step_frac": 28.0 * B * Tl * C / (ms * 1e-3) / 1e9 / peak,
-            "launch": "eager launches, NCCL all-gather of the summaries inside every step",
+            "launch": launch,
             "matches_single_gpu": bool(flags[0].item() == 1.0), "max_scaled_err_vs_single_gpu": -flags[1].item(),
             "against": "the same sequence through the kernels of one GPU (every rank runs it whole), all of y, gr, gk, gv, gw, gu"}
 
