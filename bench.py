@@ -57,7 +57,7 @@ def parse():
                          "0 = automatic: 1 when a rank has at least 256 (batch, head) sequences, else enough to reach 256")
     ap.add_argument("--tshard", action="store_true",
                     help="shard T over the ranks (long sequences): states are carried rank to rank; implies weak=False")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate", "shift_mix", "lm_loss", "train_step", "inference"],
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "gn_gate", "shift_mix", "channel_mix_act", "lm_loss", "train_step", "inference"],
                     help="train: the headline metric (fwd+bwd).  decode: single-token state updates of an inference step "
                          "(B16 H64 N64, one fp32 state per layer, --layers of them, replayed from a CUDA graph).  gn_gate: the "
                          "fused per-head GroupNorm + gate after the WKV op, forward + backward, at the B, T, H of config 1.  shift_mix: the "
@@ -896,6 +896,64 @@ def run_shift_mix(a):
     }), flush=True)
 
 
+def run_channel_mix_act(a):
+    """One step = forward + backward of the two channel-mix activations at the training shape: relu_sq on
+    [B*T, 7168] (ffn width of the 1.6B shape, scaled with H*N) and sigmoid_mul on [B*T, H*N], bf16."""
+    import ctypes
+    import torch
+    from star_rwkv6_b200._lib import check, lib
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    rows, D = a.B * a.T, a.H * a.N
+    FF = 7168 * D // 2048
+    g = torch.Generator(device=dev).manual_seed(0)
+    mk = lambda n, s=1.0: (torch.randn(rows, n, generator=g, device=dev) * s).to(torch.bfloat16)
+    sets = [dict(x=mk(FF, 2.0), gk=mk(FF), r=mk(D, 3.0), kv=mk(D), go=mk(D)) for _ in range(2)]   # 1.1 GB per set
+    outs = dict(k=torch.empty(rows, FF, dtype=torch.bfloat16, device=dev), gx=torch.empty(rows, FF, dtype=torch.bfloat16, device=dev),
+                o=torch.empty(rows, D, dtype=torch.bfloat16, device=dev), gr=torch.empty(rows, D, dtype=torch.bfloat16, device=dev),
+                gkv=torch.empty(rows, D, dtype=torch.bfloat16, device=dev))
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def fwd(d):
+        check(lib.wkv6_relu_sq_forward(rows * FF, 0, p(d["x"]), p(outs["k"]), st))
+        check(lib.wkv6_sigmoid_mul_forward(rows * D, 0, p(d["r"]), p(d["kv"]), p(outs["o"]), st))
+
+    def bwd(d):
+        check(lib.wkv6_relu_sq_backward(rows * FF, 0, p(d["x"]), p(d["gk"]), p(outs["gx"]), st))
+        check(lib.wkv6_sigmoid_mul_backward(rows * D, 0, p(d["r"]), p(d["kv"]), p(d["go"]), p(outs["gr"]), p(outs["gkv"]), st))
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    for i in range(max(3, a.warmup)):
+        fwd(sets[i % 2]); bwd(sets[i % 2])
+    torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(a.steps)]
+    for i in range(a.steps):
+        ev[i][0].record(); fwd(sets[i % 2]); ev[i][1].record(); bwd(sets[i % 2]); ev[i][2].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    ms = ev[0][0].elapsed_time(ev[-1][2]) / a.steps
+    fwd_bytes = 2 * (2 * rows * FF + 3 * rows * D)
+    bwd_bytes = 2 * (3 * rows * FF + 5 * rows * D)
+    peak, peak_src = measured_peak()
+    print(json.dumps({
+        "metric": "channel_mix_act_fwd_bwd_mtokens_per_s", "value": rows / (ms * 1e-3) / 1e6, "unit": "Mtokens/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": max(3, a.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"channel-mix activations fwd+bwd: relu_sq on [{rows}, {FF}], sigmoid_mul on [{rows}, {D}], bf16",
+                   "l2": "two rotating input sets of 1.1 GB each, larger than the 126 MB L2"},
+        "roofline": {"bound": "hbm", "kernel": "channel_mix_elementwise_kernel (backward pair)", "achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s", "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": None,
+                     "peak_source": peak_src, "algorithmic_bytes_per_launch": bwd_bytes, "avg_ms": bwd_ms,
+                     "forward": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
+                                 "algorithmic_bytes_per_launch": fwd_bytes, "avg_ms": fwd_ms}},
+        "clocks": clocks, "gpu_launches": 4 * a.steps,
+    }), flush=True)
+
+
 def run_lm_loss(a):
     """One step = the fused language-model loss (softmax cross-entropy + logit gradient, one kernel) over 8192 x 65536
     bf16 logits; two rotating buffers of 1.07 GB each, larger than the 126 MB L2."""
@@ -1156,6 +1214,8 @@ def main():
         run_gn_gate(a)
     elif a.workload == "shift_mix":
         run_shift_mix(a)
+    elif a.workload == "channel_mix_act":
+        run_channel_mix_act(a)
     elif a.workload == "lm_loss":
         run_lm_loss(a)
     elif a.workload == "train_step":

@@ -267,6 +267,21 @@ WKV6_API int wkv6_shift_mix_backward(int32_t B, int32_t T, int32_t C, int32_t dt
 WKV6_API size_t wkv6_shift_mix_workspace_bytes(int32_t B, int32_t T, int32_t C, int32_t m_is_vector);
 
 /*
+ * Activations of the channel-mix block over whole sequences, one launch per direction (n elements of `dtype`, dense,
+ * pointers 16-byte aligned):
+ *   wkv6_relu_sq_forward:      out = max(x, 0)^2          wkv6_relu_sq_backward:      gx = gout * 2 max(x, 0)
+ *   wkv6_sigmoid_mul_forward:  out = sigmoid(r) * kv      wkv6_sigmoid_mul_backward:  gr = gout * kv * s (1 - s), gkv = gout * s
+ * They replace the framework operations behind the reference's ChannelMix (rwkv6_model.py:47-48 relu_square as the
+ * activation of dense_key, :83 sigmoid as the activation of dense_receptance, :64 `o = r * kv`) and their autograd
+ * kernels: operands read once, results written once.
+ */
+WKV6_API int wkv6_relu_sq_forward(int64_t n, int32_t dtype, const void *x, void *out, void *stream);
+WKV6_API int wkv6_relu_sq_backward(int64_t n, int32_t dtype, const void *x, const void *gout, void *gx, void *stream);
+WKV6_API int wkv6_sigmoid_mul_forward(int64_t n, int32_t dtype, const void *r, const void *kv, void *out, void *stream);
+WKV6_API int wkv6_sigmoid_mul_backward(int64_t n, int32_t dtype, const void *r, const void *kv, const void *gout, void *gr,
+                                       void *gkv, void *stream);
+
+/*
  * Pitched copy between host and device memory on `stream` (a thin wrapper of cudaMemcpy2DAsync, exported so that a
  * host-side pipeline bound through this ABI needs no second library): `rows` lines of `width_bytes` bytes, line i at
  * dst + i*dst_pitch / src + i*src_pitch.  to_host = 0: host to device, 1: device to host.  A head group of a [T, H*N]

@@ -24,6 +24,7 @@ SYMBOLS = (
     "wkv6_decode_sigmoid_mul_add", "wkv6_softmax_xent_bf16", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
     "wkv6_groupnorm_gate_forward", "wkv6_groupnorm_gate_backward", "wkv6_groupnorm_gate_workspace_bytes",
     "wkv6_shift_mix_forward", "wkv6_shift_mix_backward", "wkv6_shift_mix_workspace_bytes", "wkv6_copy_2d_async",
+    "wkv6_relu_sq_forward", "wkv6_relu_sq_backward", "wkv6_sigmoid_mul_forward", "wkv6_sigmoid_mul_backward",
     "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_forward_ckpt", "wkv6_xla_backward_ws",
     "wkv6_xla_buffer_bytes", "wkv6_xla_descriptor", "wkv6_xla_target",
 )
@@ -107,6 +108,11 @@ def _load():
     lib.wkv6_shift_mix_backward.argtypes = [i32] * 6 + [vp] * 6 + [sz, vp]
     lib.wkv6_shift_mix_workspace_bytes.restype = sz
     lib.wkv6_shift_mix_workspace_bytes.argtypes = [i32] * 4
+    for name, nptr in (("wkv6_relu_sq_forward", 2), ("wkv6_relu_sq_backward", 3), ("wkv6_sigmoid_mul_forward", 3),
+                       ("wkv6_sigmoid_mul_backward", 5)):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [i64, i32] + [vp] * nptr + [vp]
     lib.wkv6_copy_2d_async.restype = ctypes.c_int
     lib.wkv6_copy_2d_async.argtypes = [vp, sz, vp, sz, sz, sz, i32, vp]
     lib.wkv6_xla_buffer_bytes.restype = sz

@@ -13,6 +13,7 @@ import torch
 from torch import nn
 
 from . import decode_stages as ds
+from .channel_mix_ops import relu_sq, sigmoid_mul
 from .group_norm import GroupNormGate
 from .group_norm import groupnorm_gate_forward_raw
 from .ops import wkv6, wkv6_decode, wkv6_with_state
@@ -167,8 +168,8 @@ class ChannelMix(nn.Module):
     def forward(self, x):
         xk = shift_mix_vector(x, self.time_mix_k)
         xr = shift_mix_vector(x, self.time_mix_r)
-        k = torch.relu(self.dense_key(xk)) ** 2
-        return torch.sigmoid(self.dense_receptance(xr)) * self.dense_value(k)
+        k = relu_sq(self.dense_key(xk))                                   # one kernel per direction instead of relu, pow
+        return sigmoid_mul(self.dense_receptance(xr), self.dense_value(k))   # ... and of sigmoid, mul
 
     @torch.no_grad()
     def prefill(self, x):
