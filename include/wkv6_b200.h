@@ -248,6 +248,16 @@ WKV6_API int wkv6_groupnorm_gate_backward(int64_t rows, int32_t H, int32_t N, in
                                           void *gy, void *gg, float *gscale, float *goffset, void *workspace,
                                           size_t workspace_bytes, void *stream);
 WKV6_API size_t wkv6_groupnorm_gate_workspace_bytes(int64_t rows, int32_t H, int32_t N);
+/* The same stage with the gate's activation inside: g_raw is the gate projection before SiLU (rwkv6_model.py:147
+ * `g = silu(dense_g(xg))`), out = (...) * silu(g_raw), and the backward returns the gradient of g_raw.  The activated
+ * gate is never written to memory.  All other arguments as above. */
+WKV6_API int wkv6_groupnorm_silu_gate_forward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y,
+                                              const void *g_raw, const float *scale, const float *offset, void *out,
+                                              void *stream);
+WKV6_API int wkv6_groupnorm_silu_gate_backward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y,
+                                               const void *g_raw, const float *scale, const float *offset, const void *gout,
+                                               void *gy, void *gg_raw, float *gscale, float *goffset, void *workspace,
+                                               size_t workspace_bytes, void *stream);
 
 /*
  * Input stage of the time-mix block: token-shift interpolations

@@ -43,6 +43,24 @@ def backward(y, g, scale, offset, gout, eps=EPSILON):
     return gy.reshape(np.shape(y)), gg.reshape(np.shape(y)), gscale, goffset
 
 
+def _silu(x):
+    x = np.asarray(x, np.float64)
+    return x / (1.0 + np.exp(-x))
+
+
+def forward_silu(y, g_raw, scale, offset, eps=EPSILON):
+    """The same stage with the gate's SiLU inside (rwkv6_model.py:147 `g = silu(dense_g(xg))`)."""
+    return forward(y, _silu(g_raw), scale, offset, eps)
+
+
+def backward_silu(y, g_raw, scale, offset, gout, eps=EPSILON):
+    """Gradients with respect to y, g_raw, scale, offset."""
+    x = np.asarray(g_raw, np.float64)
+    s = 1.0 / (1.0 + np.exp(-x))
+    gy, gg, gscale, goffset = backward(y, x * s, scale, offset, gout, eps)
+    return gy, gg * (s * (1.0 + x * (1.0 - s))).reshape(np.shape(gg)), gscale, goffset
+
+
 def make_inputs(rows, H, N, seed=0):
     """y with the scale of WKV outputs at the benchmark distributions (std about 0.03), a silu-activated gate,
     scale near one, small offset, unit-variance output gradient."""

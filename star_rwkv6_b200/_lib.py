@@ -23,6 +23,7 @@ SYMBOLS = (
     "wkv6_decode", "wkv6_decode_gated", "wkv6_decode_ln_shift_mix", "wkv6_decode_lora_mix", "wkv6_decode_relu_sq",
     "wkv6_decode_sigmoid_mul_add", "wkv6_softmax_xent_bf16", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded",
     "wkv6_groupnorm_gate_forward", "wkv6_groupnorm_gate_backward", "wkv6_groupnorm_gate_workspace_bytes",
+    "wkv6_groupnorm_silu_gate_forward", "wkv6_groupnorm_silu_gate_backward",
     "wkv6_shift_mix_forward", "wkv6_shift_mix_backward", "wkv6_shift_mix_workspace_bytes", "wkv6_copy_2d_async",
     "wkv6_relu_sq_forward", "wkv6_relu_sq_backward", "wkv6_sigmoid_mul_forward", "wkv6_sigmoid_mul_backward",
     "wkv6_xla_forward", "wkv6_xla_backward", "wkv6_xla_forward_with_state", "wkv6_xla_forward_ckpt", "wkv6_xla_backward_ws",
@@ -100,6 +101,10 @@ def _load():
     lib.wkv6_groupnorm_gate_forward.argtypes = [i64, i32, i32, i32, ctypes.c_float, vp, vp, vp, vp, vp, vp]
     lib.wkv6_groupnorm_gate_backward.restype = ctypes.c_int
     lib.wkv6_groupnorm_gate_backward.argtypes = [i64, i32, i32, i32, ctypes.c_float] + [vp] * 10 + [sz, vp]
+    lib.wkv6_groupnorm_silu_gate_forward.restype = ctypes.c_int
+    lib.wkv6_groupnorm_silu_gate_forward.argtypes = [i64, i32, i32, i32, ctypes.c_float, vp, vp, vp, vp, vp, vp]
+    lib.wkv6_groupnorm_silu_gate_backward.restype = ctypes.c_int
+    lib.wkv6_groupnorm_silu_gate_backward.argtypes = [i64, i32, i32, i32, ctypes.c_float] + [vp] * 10 + [sz, vp]
     lib.wkv6_groupnorm_gate_workspace_bytes.restype = sz
     lib.wkv6_groupnorm_gate_workspace_bytes.argtypes = [i64, i32, i32]
     lib.wkv6_shift_mix_forward.restype = ctypes.c_int

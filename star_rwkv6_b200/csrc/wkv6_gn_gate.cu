@@ -83,7 +83,9 @@ __device__ __forceinline__ void head_stats(const float (&y)[8], float eps, float
     rstd = rsqrtf(head_sum(q) * (1.0f / 64.0f) + eps);
 }
 
-template <typename T>
+// SILU: g is the gate projection before its activation and the kernel applies silu(g) = g sigmoid(g) itself
+// (rwkv6_model.py:147 `g = silu(dense_g(xg))`), so that the activated gate never exists in memory.
+template <typename T, bool SILU>
 __global__ void __launch_bounds__(1024) gn_gate_fwd_kernel(int64_t rows, int C, float eps, const void *__restrict__ y,
                                                            const void *__restrict__ g, const float *__restrict__ scale,
                                                            const float *__restrict__ offset, void *__restrict__ out) {
@@ -104,12 +106,15 @@ __global__ void __launch_bounds__(1024) gn_gate_fwd_kernel(int64_t rows, int C, 
         float mean, rstd;
         head_stats(yv, eps, mean, rstd);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = fmaf((yv[e] - mean) * rstd, sc[e], of[e]) * gv[e];
+        for (int e = 0; e < 8; ++e) {
+            const float gate = SILU ? gv[e] / (1.f + __expf(-gv[e])) : gv[e];
+            o[e] = fmaf((yv[e] - mean) * rstd, sc[e], of[e]) * gate;
+        }
         if (live) Vec8<T>::store(out, i, o);
     }
 }
 
-template <typename T>
+template <typename T, bool SILU>
 __global__ void __launch_bounds__(1024) gn_gate_bwd_kernel(int64_t rows, int C, float eps, const void *__restrict__ y,
                                                            const void *__restrict__ g, const float *__restrict__ scale,
                                                            const float *__restrict__ offset, const void *__restrict__ gout,
@@ -139,8 +144,14 @@ __global__ void __launch_bounds__(1024) gn_gate_bwd_kernel(int64_t rows, int C, 
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             xh[e] = (yv[e] - mean) * rstd;
-            const float gog = go[e] * gv[e];
-            dg[e] = go[e] * fmaf(xh[e], sc[e], of[e]);
+            float gate = gv[e], dgate = 1.f;  // silu(g) = g s, its derivative s (1 + g (1 - s)), s = sigmoid(g)
+            if (SILU) {
+                const float sg = 1.f / (1.f + __expf(-gv[e]));
+                gate = gv[e] * sg;
+                dgate = sg * fmaf(gv[e], 1.f - sg, 1.f);
+            }
+            const float gog = go[e] * gate;
+            dg[e] = go[e] * fmaf(xh[e], sc[e], of[e]) * dgate;
             dx[e] = gog * sc[e];
             dsc[e] = fmaf(gog, xh[e], dsc[e]);
             dof[e] += gog;
@@ -207,20 +218,33 @@ using namespace wkv6;
 
 extern "C" {
 
-__attribute__((visibility("default")))
-int wkv6_groupnorm_gate_forward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y, const void *g,
-                                const float *scale, const float *offset, void *out, void *stream) {
+extern "C++" {
+template <bool SILU>
+static int gn_forward_impl(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y, const void *g,
+                           const float *scale, const float *offset, void *out, void *stream) {
     int rc = gn_check(rows, H, N, dtype, "wkv6_groupnorm_gate_forward");
     if (rc) return rc;
     if (rows == 0) return WKV6_OK;
     GN_PTR(y); GN_PTR(g); GN_PTR(scale); GN_PTR(offset); GN_PTR(out);
     const int C = H * N, threads = (C / kGnVec + 31) / 32 * 32, grid = gn_grid(rows);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == WKV6_BF16) gn_gate_fwd_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, out);
-    else if (dtype == WKV6_F16) gn_gate_fwd_kernel<__half><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, out);
-    else gn_gate_fwd_kernel<float><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, out);
+    if (dtype == WKV6_BF16) gn_gate_fwd_kernel<__nv_bfloat16, SILU><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, out);
+    else if (dtype == WKV6_F16) gn_gate_fwd_kernel<__half, SILU><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, out);
+    else gn_gate_fwd_kernel<float, SILU><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, out);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "gn_gate_fwd_kernel launch");
+}
+}  // extern "C++"
+
+__attribute__((visibility("default")))
+int wkv6_groupnorm_gate_forward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y, const void *g,
+                                const float *scale, const float *offset, void *out, void *stream) {
+    return gn_forward_impl<false>(rows, H, N, dtype, eps, y, g, scale, offset, out, stream);
+}
+__attribute__((visibility("default")))
+int wkv6_groupnorm_silu_gate_forward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y, const void *g_raw,
+                                     const float *scale, const float *offset, void *out, void *stream) {
+    return gn_forward_impl<true>(rows, H, N, dtype, eps, y, g_raw, scale, offset, out, stream);
 }
 
 __attribute__((visibility("default")))
@@ -229,10 +253,11 @@ size_t wkv6_groupnorm_gate_workspace_bytes(int64_t rows, int32_t H, int32_t N) {
     return (size_t)gn_grid(rows) * 2 * H * N * sizeof(float);
 }
 
-__attribute__((visibility("default")))
-int wkv6_groupnorm_gate_backward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y, const void *g,
-                                 const float *scale, const float *offset, const void *gout, void *gy, void *gg,
-                                 float *gscale, float *goffset, void *workspace, size_t workspace_bytes, void *stream) {
+extern "C++" {
+template <bool SILU>
+static int gn_backward_impl(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y, const void *g,
+                            const float *scale, const float *offset, const void *gout, void *gy, void *gg,
+                            float *gscale, float *goffset, void *workspace, size_t workspace_bytes, void *stream) {
     int rc = gn_check(rows, H, N, dtype, "wkv6_groupnorm_gate_backward");
     if (rc) return rc;
     GN_PTR(gscale); GN_PTR(goffset);
@@ -251,16 +276,33 @@ int wkv6_groupnorm_gate_backward(int64_t rows, int32_t H, int32_t N, int32_t dty
     const int grid = gn_grid(rows);
     float *partial = static_cast<float *>(workspace);
     if (dtype == WKV6_BF16)
-        gn_gate_bwd_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, gout, gy, gg, partial);
+        gn_gate_bwd_kernel<__nv_bfloat16, SILU><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, gout, gy, gg, partial);
     else if (dtype == WKV6_F16)
-        gn_gate_bwd_kernel<__half><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, gout, gy, gg, partial);
+        gn_gate_bwd_kernel<__half, SILU><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, gout, gy, gg, partial);
     else
-        gn_gate_bwd_kernel<float><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, gout, gy, gg, partial);
+        gn_gate_bwd_kernel<float, SILU><<<grid, threads, 0, st>>>(rows, C, eps, y, g, scale, offset, gout, gy, gg, partial);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gn_gate_bwd_kernel launch");
     gn_gate_reduce_kernel<<<(2 * C + 31) / 32, 256, 0, st>>>(grid, C, partial, gscale, goffset);
     e = cudaGetLastError();
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "gn_gate_reduce_kernel launch");
+}
+}  // extern "C++"
+
+__attribute__((visibility("default")))
+int wkv6_groupnorm_gate_backward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y, const void *g,
+                                 const float *scale, const float *offset, const void *gout, void *gy, void *gg,
+                                 float *gscale, float *goffset, void *workspace, size_t workspace_bytes, void *stream) {
+    return gn_backward_impl<false>(rows, H, N, dtype, eps, y, g, scale, offset, gout, gy, gg, gscale, goffset, workspace,
+                                   workspace_bytes, stream);
+}
+__attribute__((visibility("default")))
+int wkv6_groupnorm_silu_gate_backward(int64_t rows, int32_t H, int32_t N, int32_t dtype, float eps, const void *y,
+                                      const void *g_raw, const float *scale, const float *offset, const void *gout, void *gy,
+                                      void *gg_raw, float *gscale, float *goffset, void *workspace, size_t workspace_bytes,
+                                      void *stream) {
+    return gn_backward_impl<true>(rows, H, N, dtype, eps, y, g_raw, scale, offset, gout, gy, gg_raw, gscale, goffset, workspace,
+                                  workspace_bytes, stream);
 }
 
 }  // extern "C"

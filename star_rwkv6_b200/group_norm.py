@@ -22,19 +22,21 @@ def _rows(y: torch.Tensor, H: int, N: int) -> int:
     return y.numel() // (H * N)
 
 
-def groupnorm_gate_forward_raw(y, g, scale, offset, eps: float = EPSILON):
+def groupnorm_gate_forward_raw(y, g, scale, offset, eps: float = EPSILON, gate_is_raw: bool = False):
+    """``gate_is_raw``: g is the gate projection before its SiLU (rwkv6_model.py:147) and the kernel applies it."""
     _check_cuda(y, g, scale, offset)
     H, N = scale.shape
     assert g.shape == y.shape and g.dtype == y.dtype and g.is_contiguous()
     assert scale.dtype == torch.float32 and offset.dtype == torch.float32 and offset.shape == scale.shape
     out = torch.empty_like(y)
     with torch.cuda.device(y.device):
-        check(lib.wkv6_groupnorm_gate_forward(_rows(y, H, N), H, N, _DT[y.dtype], eps, _ptr(y), _ptr(g), _ptr(scale.contiguous()),
-                                              _ptr(offset.contiguous()), _ptr(out), _stream(y.device)))
+        fn = lib.wkv6_groupnorm_silu_gate_forward if gate_is_raw else lib.wkv6_groupnorm_gate_forward
+        check(fn(_rows(y, H, N), H, N, _DT[y.dtype], eps, _ptr(y), _ptr(g), _ptr(scale.contiguous()),
+                 _ptr(offset.contiguous()), _ptr(out), _stream(y.device)))
     return out
 
 
-def groupnorm_gate_backward_raw(y, g, scale, offset, gout, eps: float = EPSILON):
+def groupnorm_gate_backward_raw(y, g, scale, offset, gout, eps: float = EPSILON, gate_is_raw: bool = False):
     _check_cuda(y, g, scale, offset, gout)
     H, N = scale.shape
     rows = _rows(y, H, N)
@@ -45,29 +47,30 @@ def groupnorm_gate_backward_raw(y, g, scale, offset, gout, eps: float = EPSILON)
     nbytes = lib.wkv6_groupnorm_gate_workspace_bytes(rows, H, N)
     ws = torch.empty((max(nbytes, 16),), dtype=torch.uint8, device=y.device)
     with torch.cuda.device(y.device):
-        check(lib.wkv6_groupnorm_gate_backward(rows, H, N, _DT[y.dtype], eps, _ptr(y), _ptr(g), _ptr(scale.contiguous()),
-                                               _ptr(offset.contiguous()), _ptr(gout), _ptr(gy), _ptr(gg), _ptr(gscale),
-                                               _ptr(goffset), _ptr(ws), nbytes, _stream(y.device)))
+        fn = lib.wkv6_groupnorm_silu_gate_backward if gate_is_raw else lib.wkv6_groupnorm_gate_backward
+        check(fn(rows, H, N, _DT[y.dtype], eps, _ptr(y), _ptr(g), _ptr(scale.contiguous()),
+                 _ptr(offset.contiguous()), _ptr(gout), _ptr(gy), _ptr(gg), _ptr(gscale),
+                 _ptr(goffset), _ptr(ws), nbytes, _stream(y.device)))
     return gy, gg, gscale, goffset
 
 
 class _GroupNormGate(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, y, g, scale, offset, eps):
+    def forward(ctx, y, g, scale, offset, eps, gate_is_raw):
         ctx.save_for_backward(y, g, scale, offset)
-        ctx.eps = eps
-        return groupnorm_gate_forward_raw(y, g, scale, offset, eps)
+        ctx.eps, ctx.gate_is_raw = eps, gate_is_raw
+        return groupnorm_gate_forward_raw(y, g, scale, offset, eps, gate_is_raw)
 
     @staticmethod
     def backward(ctx, gout):
         y, g, scale, offset = ctx.saved_tensors
-        gy, gg, gs, go = groupnorm_gate_backward_raw(y, g, scale, offset, gout.to(y.dtype), ctx.eps)
-        return gy, gg, gs.to(scale.dtype), go.to(offset.dtype), None
+        gy, gg, gs, go = groupnorm_gate_backward_raw(y, g, scale, offset, gout.to(y.dtype), ctx.eps, ctx.gate_is_raw)
+        return gy, gg, gs.to(scale.dtype), go.to(offset.dtype), None, None
 
 
-def groupnorm_gate(y, g, scale, offset, eps: float = EPSILON):
-    """(scale * LN_head(y) + offset) * g, differentiable in y, g, scale, offset."""
-    return _GroupNormGate.apply(y.contiguous(), g.contiguous(), scale, offset, eps)
+def groupnorm_gate(y, g, scale, offset, eps: float = EPSILON, gate_is_raw: bool = False):
+    """(scale * LN_head(y) + offset) * g - or * silu(g) with ``gate_is_raw`` -, differentiable in y, g, scale, offset."""
+    return _GroupNormGate.apply(y.contiguous(), g.contiguous(), scale, offset, eps, gate_is_raw)
 
 
 class GroupNormGate(torch.nn.Module):
@@ -81,5 +84,6 @@ class GroupNormGate(torch.nn.Module):
         self.scale = torch.nn.Parameter(torch.ones(self.num_heads, head_size))
         self.offset = torch.nn.Parameter(torch.zeros(self.num_heads, head_size))
 
-    def forward(self, x, g):
-        return groupnorm_gate(x, g, self.scale, self.offset, self.epsilon)
+    def forward(self, x, g, gate_is_raw: bool = False):
+        """``gate_is_raw=True``: g is ``dense_g(xg)`` before SiLU and ``forward(x, g) == group_norm(x) * silu(g)``."""
+        return groupnorm_gate(x, g, self.scale, self.offset, self.epsilon, gate_is_raw)

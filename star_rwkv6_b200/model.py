@@ -82,9 +82,8 @@ class TimeMix(nn.Module):
         xr, xk, xv, xw, xg = self.mix_inputs(x)
         r, k, v = self.dense_r(xr), self.dense_k(xk), self.dense_v(xv)
         w = self.w_b(torch.tanh(self.w_a(xw)))
-        g = torch.nn.functional.silu(self.dense_g(xg))
         y = wkv6(r, k, v, w, self.time_faaaa, self.head_size)
-        return self.dense_o(self.group_norm(y, g))
+        return self.dense_o(self.group_norm(y, self.dense_g(xg), gate_is_raw=True))   # SiLU of the gate inside the kernel
 
     def _project(self, xr, xk, xv, xw, xg):
         r, k, v = self.dense_r(xr), self.dense_k(xk), self.dense_v(xv)

@@ -35,6 +35,22 @@ def test_oracle_edge_cases():
     assert np.allclose(out, np.tile(d["offset"].reshape(1, -1), (3, 1)) * d["g"], atol=1e-12)
 
 
+def test_oracle_silu_gate_matches_autograd():
+    """The stage with the gate's SiLU inside, pinned on torch float64 autograd over the reference's expressions
+    (rwkv6_model.py:147 silu(dense_g(.)), :93-99 GroupNorm, :158-160 the product)."""
+    import torch
+    H, N, rows = 2, 64, 5
+    d = G.make_inputs(rows, H, N, seed=3)
+    t = {k: torch.tensor(v, dtype=torch.float64).requires_grad_(k != "gout") for k, v in d.items()}
+    xh = torch.nn.functional.layer_norm(t["y"].reshape(rows, H, N), (N,), eps=G.EPSILON)
+    out = ((xh * t["scale"] + t["offset"]).reshape(rows, H * N)) * torch.nn.functional.silu(t["g"])
+    (out * t["gout"]).sum().backward()
+    assert np.abs(G.forward_silu(d["y"], d["g"], d["scale"], d["offset"]) - out.detach().numpy()).max() <= 1e-12
+    got = G.backward_silu(d["y"], d["g"], d["scale"], d["offset"], d["gout"])
+    for a, b in zip(got, (t["y"].grad, t["g"].grad, t["scale"].grad, t["offset"].grad)):
+        assert np.abs(a - b.numpy()).max() <= 1e-10 * max(1.0, float(b.abs().max()))
+
+
 # ---- GPU parity (bf16: max error relative to max|ref| <= 2e-2; fp32: <= 1e-4, the tolerances of the WKV path) ------
 
 def _scaled_err(got, ref):
@@ -63,6 +79,26 @@ def test_gpu_vs_oracle(rows, H, dtype):
     for name, got, want in zip(("gy", "gg", "gscale", "goffset"), (gy, gg, gs, go), ref):
         assert np.isfinite(got.float().cpu().numpy()).all(), name
         assert _scaled_err(got.float().cpu().numpy(), want) <= tol, name
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,H,dtype", [(7, 2, "f32"), (1000, 32, "bf16"), (100, 5, "f16")])
+def test_gpu_silu_gate_vs_oracle(rows, H, dtype):
+    import torch
+    from star_rwkv6_b200 import group_norm as M
+    N = 64
+    tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[dtype]
+    tol = 1e-4 if dtype == "f32" else 2e-2
+    d = G.make_inputs(rows, H, N, seed=rows + H)
+    d["g"] = np.random.default_rng(rows).standard_normal((rows, H * N)).astype(np.float32) * 2   # the raw gate projection
+    t = {k: torch.tensor(v).to(tdt).cuda() for k, v in d.items() if k in ("y", "g", "gout")}
+    scale, offset = torch.tensor(d["scale"]).cuda(), torch.tensor(d["offset"]).cuda()
+    rd = {k: t[k].float().cpu().numpy() for k in t}
+    out = M.groupnorm_gate_forward_raw(t["y"], t["g"], scale, offset, gate_is_raw=True)
+    got = M.groupnorm_gate_backward_raw(t["y"], t["g"], scale, offset, t["gout"], gate_is_raw=True)
+    assert _scaled_err(out.float().cpu().numpy(), G.forward_silu(rd["y"], rd["g"], d["scale"], d["offset"])) <= tol
+    for name, a, want in zip(("gy", "gg_raw", "gscale", "goffset"), got, G.backward_silu(rd["y"], rd["g"], d["scale"], d["offset"], rd["gout"])):
+        assert _scaled_err(a.float().cpu().numpy(), want) <= tol, name
 
 
 @pytest.mark.gpu
