@@ -86,9 +86,12 @@ int wkv6_copy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_
     if (dst == nullptr || src == nullptr) return fail(WKV6_ERR_INVALID, "wkv6_copy_2d_async: NULL pointer");
     if (dst_pitch < width_bytes || src_pitch < width_bytes)
         return fail(WKV6_ERR_INVALID, "wkv6_copy_2d_async: a pitch is smaller than the line width");
-    cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
-                                      to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice,
-                                      static_cast<cudaStream_t>(stream));
+    const cudaMemcpyKind kind = to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice;
+    cudaError_t e;
+    if (dst_pitch == width_bytes && src_pitch == width_bytes)  // one contiguous block: a plain copy
+        e = cudaMemcpyAsync(dst, src, width_bytes * rows, kind, static_cast<cudaStream_t>(stream));
+    else
+        e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, kind, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "cudaMemcpy2DAsync");
 }
 
