@@ -149,7 +149,8 @@ def run_reference(a):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
         "warmup": a.warmup, "ms_per_step": 1e3 * total / len(timed), "higher_is_better": True,
         "scaling": a.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(a), "note": "reference algorithm on the host cores only"},
+        "config": {"workload": workload_name(a)},
+        "setup": {"note": "reference algorithm on the host cores only"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": sample_text(a, pairs) + " per step"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -569,10 +570,11 @@ def run_b200(a):
             "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if (a.tshard or strong or world == 1 and a.scaling == "strong") else "weak", "vs_baseline": None,
             "dtype": "bf16" if a.dtype == "bf16" else "f32", "data": "synthetic",
-            "config": {"workload": workload_name(a), "per_gpu": f"B{B} T{T} H{H} N{N}", "variant": vname,
+            "config": {"workload": workload_name(a),
+                       "l2": f"two rotating input sets; a step touches {(5 + 5 + 1) * elems * esz / 1e6:.0f} MB per GPU (5 inputs, 5 outputs, "
+                             "checkpoints), more than the 126 MB L2, and the next step uses the other set"},
+            "setup": {"per_gpu": f"B{B} T{T} H{H} N{N}", "variant": vname,
                        "u_dtype": "f32", "state": "f32",
-                       "l2": f"two rotating input sets of {5 * elems * esz / 1e6:.0f} MB each per GPU"
-                             + (", larger than the 126 MB L2" if 5 * elems * esz > 126e6 else " (smaller than the 126 MB L2: the split leaves each GPU less than one L2 of inputs)"),
                        "segments_per_sequence": a.segments,
                        "launch": launch_mode,
                        "parallelism": par},
