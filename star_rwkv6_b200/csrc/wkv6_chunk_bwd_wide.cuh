@@ -152,6 +152,32 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     const uint32_t tmGUp = tbase + (16u << 16) + lo + 192 + 16 * half;       // 8 words of gu partial sums
     const uint32_t tmStash = tbase + (16u << 16) + lo + 224 + 16 * half;     // 8 words of bf16 log-decays
 
+    // the barriers are initialised: the last chunk's tiles are requested before the reverse state is read
+    // copy thread: loads in flight per barrier and the phase parity their completion will have
+    bool pend_w = false, pend_rk = false, pend_late = false;
+    uint32_t par_early = 0, par_rk = 0;
+    auto issue_early = [&](int c) {  // tiles that are dead once the second MMA group has completed
+        par_early = (uint32_t)(nchunks - 1 - c) & 1u;
+        mbar_expect_tx(bar_w, kTile);
+        tma_load_3d(sW, &tm_w, bar_w, h * 64, c * kChunk, b);
+        mbar_expect_tx(bar_late, 3 * kTile);
+        tma_load_3d(sV, &tm_v, bar_late, h * 64, c * kChunk, b);
+        tma_load_3d(sG, &tm_gy, bar_late, h * 64, c * kChunk, b);
+        bulk_load(sS, a.ckpt + ((size_t)blockIdx.x * nchunks + c) * 4096, kTile, bar_late);
+        pend_w = pend_late = true;
+    };
+    auto issue_rk = [&](int c) {  // tiles the second epilogue still reads
+        par_rk = (uint32_t)(nchunks - 1 - c) & 1u;
+        mbar_expect_tx(bar_rk, 2 * kTile);
+        tma_load_3d(sR, &tm_r, bar_rk, h * 64, c * kChunk, b);
+        tma_load_3d(sK, &tm_k, bar_rk, h * 64, c * kChunk, b);
+        pend_rk = true;
+    };
+    // Copies are issued by one thread of warp 4, so that warps 0-3, whose first lanes issue the MMAs, never
+    // queue behind them.
+    const bool copy_thread = (tid == 128);
+    if (copy_thread) { issue_early(nchunks - 1); issue_rk(nchunks - 1); }
+
     // the reverse state entering at the end of the sequence: fp32 copy in tensor memory, bf16 operand copy in shared memory
     {
         float AB[16];
@@ -178,30 +204,6 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     __syncthreads();
     tc_fence_after_sync();
 
-    // copy thread: loads in flight per barrier and the phase parity their completion will have
-    bool pend_w = false, pend_rk = false, pend_late = false;
-    uint32_t par_early = 0, par_rk = 0;
-    auto issue_early = [&](int c) {  // tiles that are dead once the second MMA group has completed
-        par_early = (uint32_t)(nchunks - 1 - c) & 1u;
-        mbar_expect_tx(bar_w, kTile);
-        tma_load_3d(sW, &tm_w, bar_w, h * 64, c * kChunk, b);
-        mbar_expect_tx(bar_late, 3 * kTile);
-        tma_load_3d(sV, &tm_v, bar_late, h * 64, c * kChunk, b);
-        tma_load_3d(sG, &tm_gy, bar_late, h * 64, c * kChunk, b);
-        bulk_load(sS, a.ckpt + ((size_t)blockIdx.x * nchunks + c) * 4096, kTile, bar_late);
-        pend_w = pend_late = true;
-    };
-    auto issue_rk = [&](int c) {  // tiles the second epilogue still reads
-        par_rk = (uint32_t)(nchunks - 1 - c) & 1u;
-        mbar_expect_tx(bar_rk, 2 * kTile);
-        tma_load_3d(sR, &tm_r, bar_rk, h * 64, c * kChunk, b);
-        tma_load_3d(sK, &tm_k, bar_rk, h * 64, c * kChunk, b);
-        pend_rk = true;
-    };
-    // Copies are issued by one thread of warp 4, so that warps 0-3, whose first lanes issue the MMAs, never
-    // queue behind them.
-    const bool copy_thread = (tid == 128);
-    if (copy_thread) { issue_early(nchunks - 1); issue_rk(nchunks - 1); }
 
     constexpr uint32_t idKK = umma_idesc_bf16(64, 64, false, false);
     constexpr uint32_t idKM = umma_idesc_bf16(64, 64, false, true);

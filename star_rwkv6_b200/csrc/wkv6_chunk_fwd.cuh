@@ -184,6 +184,24 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         tmem_relinquish();
     }
 
+    __syncthreads();  // the barriers are initialised: the first two chunks can be requested before the state is read
+    // Issuing a TMA copy keeps a thread busy for on the order of a hundred cycles, so the copies of one chunk are
+    // spread over warps: lane 0 of warps 2..5 loads one input tile each, lane 0 of warp 1 issues the stores.  Warp 0,
+    // whose first lane issues MMAs, issues none.
+    const int load_slot = (lane == 0 && warp >= 2 && warp <= 5) ? warp - 2 : -1;  // 0..3 = r, k, v, w
+    const int skip_chunk = *reinterpret_cast<volatile int *>(&g_skip_load_chunk);  // test hook, -1 in normal use
+    auto issue_loads = [&](int ic2) {  // every thread calls it; the four loading threads act
+        if (load_slot < 0 || ic2 == skip_chunk) return;
+        const int c = ic2;
+        const int st = ic2 & 1;
+        uint8_t *dst = smem + st * SM::kStage + load_slot * kTile;
+        const CUtensorMap *tm = load_slot == 0 ? &tm_r : load_slot == 1 ? &tm_k : load_slot == 2 ? &tm_v : &tm_w;
+        mbar_expect_tx(&bar_full[st], kTile);
+        tma_load_3d(dst, tm, &bar_full[st], h * 64, c * kChunk, b);
+    };
+    issue_loads(0);
+    if (nchunks > 1) issue_loads(1);
+
     // state in accumulator-fragment layout: rows i = ta (+8), columns j = 8(n0+nn) + 2q (+1)
     float S[16];
     {
@@ -228,23 +246,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         foB[nn] = sw128_off(ta + 8, 8 * (n0 + nn) + 2 * q);
     }
 
-    // Issuing a TMA copy keeps a thread busy for on the order of a hundred cycles, so the copies of one chunk are
-    // spread over warps: lane 0 of warps 2..5 loads one input tile each, lane 0 of warp 1 issues the stores.  Warp 0,
-    // whose first lane issues MMAs, issues none.
-    const int load_slot = (lane == 0 && warp >= 2 && warp <= 5) ? warp - 2 : -1;  // 0..3 = r, k, v, w
-    const int skip_chunk = *reinterpret_cast<volatile int *>(&g_skip_load_chunk);  // test hook, -1 in normal use
-    auto issue_loads = [&](int ic2) {  // every thread calls it; the four loading threads act
-        if (load_slot < 0 || ic2 == skip_chunk) return;
-        const int c = ic2;
-        const int st = ic2 & 1;
-        uint8_t *dst = smem + st * SM::kStage + load_slot * kTile;
-        const CUtensorMap *tm = load_slot == 0 ? &tm_r : load_slot == 1 ? &tm_k : load_slot == 2 ? &tm_v : &tm_w;
-        mbar_expect_tx(&bar_full[st], kTile);
-        tma_load_3d(dst, tm, &bar_full[st], h * 64, c * kChunk, b);
-    };
     const bool copy_thread = (tid == 32);
-    issue_loads(0);
-    if (nchunks > 1) issue_loads(1);
     if (copy_thread) {
         if (a.ckpt != nullptr) {  // state at the start of chunk 0, already in operand layout
             bulk_store(a.ckpt + (size_t)blockIdx.x * nchunks * 4096, sSB, kTile);
