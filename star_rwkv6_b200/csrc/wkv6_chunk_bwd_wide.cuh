@@ -601,21 +601,26 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         WKV6_TSTAMP(it, 10);
         // every thread has read its raw r, k: fetch the next chunk's
         if (copy_thread && c > 0 && err == 0) issue_rk(c - 1);
-        // G_t = e^{c_63} <S_in, Abar> + sum_all b + sum_{later blocks} q + (suffix_incl(q) - a)_t ;  gw = -exp(w) G
+        // G_t = e^{c_63} <S_in, Abar> + sum_all b + sum_{later blocks} q + (suffix_incl(q) - a)_t ;  gw = -exp(w) G.
+        // The part that is the same for all tokens of a block is formed once per (block, channel) by one thread.
+        {
+            const int J = tid >> 6, i = tid & 63;
+            float base = (sT1[i] + sT1[64 + i]) * sDtot[i];
+#pragma unroll
+            for (int J2 = 0; J2 < 4; ++J2) {
+                base += sBtot[J2 * 64 + i];
+                if (J2 > J) base += sXtot[J2 * 64 + i];
+            }
+            sOff[J * 64 + i] = base;
+        }
         uint32_t lwst2[8];
         tmem_ld_16x256b_x2(tmStash, lwst2);
         tmem_wait_ld();
+        __syncthreads();
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn) {
             const int col = 8 * (n0 + nn) + 2 * q;
-            const float2 t1 = add2(*reinterpret_cast<const float2 *>(&sT1[col]), *reinterpret_cast<const float2 *>(&sT1[64 + col]));
-            const float2 dt = *reinterpret_cast<const float2 *>(&sDtot[col]);
-            float2 base = mul2(t1, dt);
-#pragma unroll
-            for (int J2 = 0; J2 < 4; ++J2) {
-                base = add2(base, *reinterpret_cast<const float2 *>(&sBtot[J2 * 64 + col]));
-                if (J2 > w4) base = add2(base, *reinterpret_cast<const float2 *>(&sXtot[J2 * 64 + col]));
-            }
+            const float2 base = *reinterpret_cast<const float2 *>(&sOff[w4 * 64 + col]);
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const int e0 = 4 * nn + 2 * hrow;
