@@ -83,6 +83,18 @@ __device__ __forceinline__ void tma_store_3d(const void *tmap, const void *src, 
                  ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// 5-D forms, for tensor maps that split the token axis (x = channel, then three token sub-indices, then batch)
+__device__ __forceinline__ void tma_load_5d(void *dst, const void *tmap, uint64_t *bar, int x, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_5d(const void *tmap, const void *src, int x, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(src)), "r"(x), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+                 : "memory");
+}
 // untiled bulk copies (16-byte aligned addresses, size a multiple of 16)
 __device__ __forceinline__ void bulk_store(void *gdst, const void *src, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"

@@ -51,6 +51,25 @@ static int make_map(CUtensorMap *m, const void *base, const wkv6_problem *p, con
     return WKV6_OK;
 }
 
+// The same tensor with the token axis split as token = 16 I + 2 j + p and walked in the order (j, p, I): one box is
+// 64 channels x (8 j x 2 p x 4 I), so tile row 16 I + 8 p + j holds token 16 I + 2 j + p of the chunk (the order
+// chunk_bwd_wide_kernel<true> works in).  Needs T % 16 == 0; blocks I past the end of the sequence read as zeros
+// and are not written.
+static int make_map_paired(CUtensorMap *m, const void *base, const wkv6_problem *p, const Dims &d, const char *what) {
+    if (int rc = ensure_context()) return rc;
+    auto enc = get_encode();
+    if (!enc) return fail(WKV6_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[5] = {(cuuint64_t)d.C, 8, 2, (cuuint64_t)(p->T / 16), (cuuint64_t)p->B};
+    cuuint64_t strides[4] = {(cuuint64_t)d.ld * 4, (cuuint64_t)d.ld * 2, (cuuint64_t)d.ld * 32, (cuuint64_t)d.bs * 2};
+    cuuint32_t box[5] = {64, 8, 2, 4, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void *>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(WKV6_ERR_CUDA, "cuTensorMapEncodeTiled(%s, paired tokens) failed with CUresult %d", what, (int)r);
+    return WKV6_OK;
+}
+
 bool chunk_supported(const wkv6_problem *p) {
     return p->N == 64 && p->x_dtype == WKV6_BF16 && p->y_dtype == WKV6_BF16 && p->T >= 1;
 }
@@ -127,9 +146,25 @@ int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, c
     a.flags = flags;
     cudaError_t e;
     if (flags != nullptr) {  // the fast kernel first; it marks the sequences it has to leave to the general one
-        e = cudaFuncSetAttribute(chunk_bwd_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideBwdSmem::kAlloc);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_wide_kernel)");
-        chunk_bwd_wide_kernel<<<p->B * p->H, 256, WideBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
+        if (p->T % 16 == 0) {  // adjacent tokens per thread (see the kernel)
+            CUtensorMap pr, pk, pv, pw, pgy, pgr, pgk, pgv, pgw;
+            if ((rc = make_map_paired(&pr, r, p, d, "r"))) return rc;
+            if ((rc = make_map_paired(&pk, k, p, d, "k"))) return rc;
+            if ((rc = make_map_paired(&pv, v, p, d, "v"))) return rc;
+            if ((rc = make_map_paired(&pw, w, p, d, "w"))) return rc;
+            if ((rc = make_map_paired(&pgy, gy, p, d, "gy"))) return rc;
+            if ((rc = make_map_paired(&pgr, gr, p, d, "gr"))) return rc;
+            if ((rc = make_map_paired(&pgk, gk, p, d, "gk"))) return rc;
+            if ((rc = make_map_paired(&pgv, gv, p, d, "gv"))) return rc;
+            if ((rc = make_map_paired(&pgw, gw, p, d, "gw"))) return rc;
+            e = cudaFuncSetAttribute(chunk_bwd_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WideBwdSmem::kAlloc);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_wide_kernel)");
+            chunk_bwd_wide_kernel<true><<<p->B * p->H, 256, WideBwdSmem::kAlloc, st>>>(pr, pk, pv, pw, pgy, pgr, pgk, pgv, pgw, a);
+        } else {
+            e = cudaFuncSetAttribute(chunk_bwd_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WideBwdSmem::kAlloc);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_wide_kernel)");
+            chunk_bwd_wide_kernel<false><<<p->B * p->H, 256, WideBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
+        }
         e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "chunk_bwd_wide_kernel launch");
     }

@@ -138,6 +138,31 @@ __device__ __forceinline__ void scan_suffix16(float &a, float &b, int r0, int la
     a += __shfl_sync(0xffffffffu, b, lane & 3);
 }
 
+// The same scans when a thread holds two ADJACENT tokens of the block (a = token 2 r0, b = token 2 r0 + 1; see the token
+// order of chunk_bwd_wide_kernel): the pair is summed locally and only the pair sums travel, three shuffles per scan.
+__device__ __forceinline__ void scan_prefix16_adj(float &a, float &b, int r0) {
+    const float s = a + b;
+    float t = s;
+#pragma unroll
+    for (int d = 1; d < 8; d <<= 1) {
+        const float o = __shfl_up_sync(0xffffffffu, t, 4 * d);
+        if (r0 >= d) t += o;
+    }
+    a += t - s;  // tokens before this pair, plus a
+    b = t;       // ... plus a and b
+}
+__device__ __forceinline__ void scan_suffix16_adj(float &a, float &b, int r0) {
+    const float s = a + b;
+    float t = s;
+#pragma unroll
+    for (int d = 1; d < 8; d <<= 1) {
+        const float o = __shfl_down_sync(0xffffffffu, t, 4 * d);
+        if (r0 + d < 8) t += o;
+    }
+    b += t - s;  // tokens after this pair, plus b
+    a = t;       // ... plus a and b
+}
+
 __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant__ CUtensorMap tm_r,
                                                            const __grid_constant__ CUtensorMap tm_k,
                                                            const __grid_constant__ CUtensorMap tm_v,

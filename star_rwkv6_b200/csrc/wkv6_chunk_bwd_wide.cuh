@@ -35,7 +35,7 @@ struct WideBwdSmem {
     static constexpr int oP = oET + kTile;          // masked P (bf16); later the gr tile
     static constexpr int oAM = oP + kTile;          // masked A (bf16); later the gk tile
     static constexpr int oAB = oAM + kTile;         // bf16 copy of Abar [i][j]
-    static constexpr int oHead = oAB + kTile;       // float [4][64] log2-decay sum of the first 8 tokens of a block
+    static constexpr int oHead = oAB + kTile;       // float [4][64] scratch of the gw phase and of the final gu reduction (below)
     static constexpr int oTot = oHead + 1024;       // float [4][64] log2-decay sum of the block
     static constexpr int oOff = oTot + 1024;        // float [4][64] reference point relative to the block start
     static constexpr int oFRb = oOff + 1024;        // bf16  [64] 2^{ref}   (ref relative to the chunk start, an integer)
@@ -46,7 +46,7 @@ struct WideBwdSmem {
     static constexpr int oVG = oBonus + 512;        // float [64]
     static constexpr int oT1 = oVG + 256;           // float [2][64] <S_in, Abar>_i, one partial per column half
     static constexpr int oXtot = oTot;              // float [4][64] block sums for gw (sTot is dead by then)
-    static constexpr int oBtot = oHead;             // float [4][64] block sums for gw (sHead is dead by then)
+    static constexpr int oBtot = oHead;             // float [4][64] block sums of b for gw
     static constexpr int oGU = oHead;               // float [4][64] final reduction of gu (after the last chunk)
     static constexpr int oBar = oT1 + 512;          // w, rk, late, mma1, mma2
     static constexpr int oSlot = oBar + 48;
@@ -75,6 +75,11 @@ __device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, float (&f)[8]
     for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[e]);
 }
 
+// PERM: the tensor maps split the token axis as (j, p, I) with token = 16 I + 2 j + p and tile row = 16 I + 8 p + j, so
+// that the two rows of a thread's fragment (r0 and r0 + 8 of block I) hold the ADJACENT tokens 2 r0 and 2 r0 + 1.  Every
+// product of the kernel sums over tokens or is indexed by them row for row, so the order only shows in the causal masks
+// and in the scans along the tokens, which then need three shuffles instead of seven.  Needs T % 16 == 0.
+template <bool PERM>
 __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_r,
                                                                 const __grid_constant__ CUtensorMap tm_k,
                                                                 const __grid_constant__ CUtensorMap tm_v,
@@ -96,7 +101,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     uint8_t *sR = smem + SM::oR, *sK = smem + SM::oK, *sV = smem + SM::oV, *sW = smem + SM::oW, *sG = smem + SM::oG;
     uint8_t *sS = smem + SM::oS, *sKH = smem + SM::oKH, *sRT = smem + SM::oRT, *sKT = smem + SM::oKT;
     uint8_t *sET = smem + SM::oET, *sP = smem + SM::oP, *sAM = smem + SM::oAM, *sAB = smem + SM::oAB;
-    float *sHead = reinterpret_cast<float *>(smem + SM::oHead), *sTot = reinterpret_cast<float *>(smem + SM::oTot);
+    float *sTot = reinterpret_cast<float *>(smem + SM::oTot);
     float *sOff = reinterpret_cast<float *>(smem + SM::oOff), *sDtot = reinterpret_cast<float *>(smem + SM::oDtot);
     __nv_bfloat16 *sFRb = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oFRb);
     __nv_bfloat16 *sFKb = reinterpret_cast<__nv_bfloat16 *>(smem + SM::oFKb);
@@ -156,21 +161,29 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     // copy thread: loads in flight per barrier and the phase parity their completion will have
     bool pend_w = false, pend_rk = false, pend_late = false;
     uint32_t par_early = 0, par_rk = 0;
+    auto ld_tile = [&](void *dst, const CUtensorMap *m, uint64_t *bar, int c) {
+        if (PERM) tma_load_5d(dst, m, bar, h * 64, 0, 0, 4 * c, b);
+        else tma_load_3d(dst, m, bar, h * 64, c * kChunk, b);
+    };
+    auto st_tile = [&](const CUtensorMap *m, const void *src, int c) {
+        if (PERM) tma_store_5d(m, src, h * 64, 0, 0, 4 * c, b);
+        else tma_store_3d(m, src, h * 64, c * kChunk, b);
+    };
     auto issue_early = [&](int c) {  // tiles that are dead once the second MMA group has completed
         par_early = (uint32_t)(nchunks - 1 - c) & 1u;
         mbar_expect_tx(bar_w, kTile);
-        tma_load_3d(sW, &tm_w, bar_w, h * 64, c * kChunk, b);
+        ld_tile(sW, &tm_w, bar_w, c);
         mbar_expect_tx(bar_late, 3 * kTile);
-        tma_load_3d(sV, &tm_v, bar_late, h * 64, c * kChunk, b);
-        tma_load_3d(sG, &tm_gy, bar_late, h * 64, c * kChunk, b);
+        ld_tile(sV, &tm_v, bar_late, c);
+        ld_tile(sG, &tm_gy, bar_late, c);
         bulk_load(sS, a.ckpt + ((size_t)blockIdx.x * nchunks + c) * 4096, kTile, bar_late);
         pend_w = pend_late = true;
     };
     auto issue_rk = [&](int c) {  // tiles the second epilogue still reads
         par_rk = (uint32_t)(nchunks - 1 - c) & 1u;
         mbar_expect_tx(bar_rk, 2 * kTile);
-        tma_load_3d(sR, &tm_r, bar_rk, h * 64, c * kChunk, b);
-        tma_load_3d(sK, &tm_k, bar_rk, h * 64, c * kChunk, b);
+        ld_tile(sR, &tm_r, bar_rk, c);
+        ld_tile(sK, &tm_k, bar_rk, c);
         pend_rk = true;
     };
     // Copies are issued by one thread of warp 4, so that warps 0-3, whose first lanes issue the MMAs, never
@@ -238,7 +251,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                     float2 l2 = mul2(make_float2(ex2f(e2.x), ex2f(e2.y)), make_float2(-kLog2e, -kLog2e));
                     l2.x = fmaxf(l2.x, kMinLogDecay2);
                     l2.y = fmaxf(l2.y, kMinLogDecay2);
-                    if (!full_chunk && c * kChunk + ta + 8 * hrow >= a.T) l2 = make_float2(0.f, 0.f);
+                    if (!full_chunk && c * kChunk + (PERM ? 16 * w4 + 2 * r0 + hrow : ta + 8 * hrow) >= a.T) l2 = make_float2(0.f, 0.f);
                     lw[4 * nn + 2 * hrow] = l2.x;
                     lw[4 * nn + 2 * hrow + 1] = l2.y;
                     { const __nv_bfloat162 lb = to_bf2(l2); lwst[2 * nn + hrow] = *reinterpret_cast<const uint32_t *>(&lb); }
@@ -251,7 +264,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 float pa = lw[4 * nn + e], pb = lw[4 * nn + 2 + e];
-                scan_prefix16(pa, pb, r0, lane);
+                if (PERM) scan_prefix16_adj(pa, pb, r0); else scan_prefix16(pa, pb, r0, lane);
                 cs[4 * nn + e] = pa;
                 cs[4 * nn + 2 + e] = pb;
             }
@@ -259,7 +272,6 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 const int col = 8 * (n0 + nn) + 2 * q;
-                *reinterpret_cast<float2 *>(&sHead[w4 * 64 + col]) = make_float2(cs[4 * nn], cs[4 * nn + 1]);
                 *reinterpret_cast<float2 *>(&sTot[w4 * 64 + col]) = make_float2(cs[4 * nn + 2], cs[4 * nn + 3]);
             }
         }
@@ -400,12 +412,21 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                         if (c1 == r0) sVG[ta] = x01;
                         x00 = (c0 < r0) ? x00 : 0.f;
                         x01 = (c1 < r0) ? x01 : 0.f;
+                        if (PERM) {               // columns are tokens 2 c, rows tokens 2 r0 and 2 r0 + 1
+                            x10 = (c0 <= r0) ? x10 : 0.f;
+                            x11 = (c1 <= r0) ? x11 : 0.f;
+                        }
                     } else {                      // columns 8..15: row r0 lies above, row r0 + 8 needs the test
                         if (c0 == r0) sVG[ta + 8] = x10;
                         if (c1 == r0) sVG[ta + 8] = x11;
                         x10 = (c0 < r0) ? x10 : 0.f;
                         x11 = (c1 < r0) ? x11 : 0.f;
-                        x00 = x01 = 0.f;
+                        if (PERM) {               // columns are tokens 2 c + 1
+                            x00 = (c0 < r0) ? x00 : 0.f;
+                            x01 = (c1 < r0) ? x01 : 0.f;
+                        } else {
+                            x00 = x01 = 0.f;
+                        }
                     }
                 }
                 *reinterpret_cast<uint32_t *>(sP + FO(nn, 0)) = pack_bf2(x00, x01);
@@ -430,7 +451,14 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                         g8[1] = (c1 < r0) ? g8[1] : (c1 == r0 ? bonus_a : 0.f);
                         g8[6] = (c0 < r0) ? g8[6] : (c0 == r0 ? bonus_b : 0.f);
                         g8[7] = (c1 < r0) ? g8[7] : (c1 == r0 ? bonus_b : 0.f);
-                        g8[4] = g8[5] = 0.f;
+                        if (PERM) {
+                            g8[2] = (c0 <= r0) ? g8[2] : 0.f;
+                            g8[3] = (c1 <= r0) ? g8[3] : 0.f;
+                            g8[4] = (c0 < r0) ? g8[4] : 0.f;
+                            g8[5] = (c1 < r0) ? g8[5] : 0.f;
+                        } else {
+                            g8[4] = g8[5] = 0.f;
+                        }
                     }
                     o0 = pack_bf2(g8[0], g8[1]); o2 = pack_bf2(g8[2], g8[3]);
                     o1 = pack_bf2(g8[4], g8[5]); o3 = pack_bf2(g8[6], g8[7]);
@@ -554,7 +582,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     float pa = qv[e], pb = qv[2 + e];
-                    scan_suffix16(pa, pb, r0, lane);
+                    if (PERM) scan_suffix16_adj(pa, pb, r0); else scan_suffix16(pa, pb, r0, lane);
                     loc[4 * nn + e] += pa;
                     loc[4 * nn + 2 + e] += pb;
                     if (r0 == 0) sXtot[w4 * 64 + col + e] = pa;
@@ -635,10 +663,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         if (!__syncthreads_and(err == 0)) { err = err ? err : 12; break; }
         WKV6_TSTAMP(it, 11);
         if (copy_thread) {
-            tma_store_3d(&tm_gr, sP, h * 64, c * kChunk, b);
-            tma_store_3d(&tm_gk, sAM, h * 64, c * kChunk, b);
-            tma_store_3d(&tm_gv, sKT, h * 64, c * kChunk, b);
-            tma_store_3d(&tm_gw, sRT, h * 64, c * kChunk, b);
+            st_tile(&tm_gr, sP, c);
+            st_tile(&tm_gk, sAM, c);
+            st_tile(&tm_gv, sKT, c);
+            st_tile(&tm_gw, sRT, c);
             bulk_commit();
         }
     }

@@ -106,7 +106,8 @@ def test_operator_autograd_bf16(pkg):
 
 
 @pytest.mark.parametrize("B,T,H,with_ckpt", [(1, 64, 1, True), (2, 128, 2, True), (1, 320, 2, False), (2, 1000, 1, True),
-                                             (1, 1, 1, True), (1, 65, 1, False), (2, 4096, 2, True)])
+                                             (1, 1, 1, True), (1, 65, 1, False), (2, 4096, 2, True),
+                                             (1, 80, 1, True), (2, 1008, 2, False), (1, 16, 2, True)])
 def test_backward_vs_oracle(pkg, B, T, H, with_ckpt):
     d = O.make_inputs(B, T, H, N, seed=31 + T + H)
     t = dev_inputs(d)
