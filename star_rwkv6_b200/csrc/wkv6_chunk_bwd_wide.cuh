@@ -532,15 +532,21 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             float gu8[8], bs8[8];  // per-channel sums over this thread's two tokens: r k vg (for gu) and b (for gw)
 #pragma unroll
             for (int e = 0; e < 8; ++e) gu8[e] = bs8[e] = 0.f;
+            // [buffer][GR1, GR2, GK1, GK2][value]: the tensor-memory loads of the next repetition fly while this one is used
+            float acc4[2][4][4];
+            auto ld4 = [&](int buf, int nn) {
+                tmem_ld_16x256b_x1(tmP + lo + cb + 8 * nn, acc4[buf][0]);
+                tmem_ld_16x256b_x1(tmGR2 + lo + cb + 8 * nn, acc4[buf][1]);
+                tmem_ld_16x256b_x1(tmA + lo + cb + 8 * nn, acc4[buf][2]);
+                tmem_ld_16x256b_x1(tmGK2 + lo + cb + 8 * nn, acc4[buf][3]);
+            };
+            ld4(0, 0);
+            tmem_wait_ld();
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 const int col = 8 * (n0 + nn) + 2 * q;
-                float g1[4], g2[4], h1[4], h2[4];
-                tmem_ld_16x256b_x1(tmP + lo + cb + 8 * nn, g1);    // GR1
-                tmem_ld_16x256b_x1(tmGR2 + lo + cb + 8 * nn, g2);  // GR2
-                tmem_ld_16x256b_x1(tmA + lo + cb + 8 * nn, h1);    // GK1
-                tmem_ld_16x256b_x1(tmGK2 + lo + cb + 8 * nn, h2);  // GK2
-                tmem_wait_ld();
+                if (nn < 3) ld4((nn + 1) & 1, nn + 1);  // not read before the wait at the end of this repetition
+                float (&g1)[4] = acc4[nn & 1][0], (&g2)[4] = acc4[nn & 1][1], (&h1)[4] = acc4[nn & 1][2], (&h2)[4] = acc4[nn & 1][3];
                 const float2 fr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&sFRb[col]));
                 const float2 fk = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&sFKb[col]));
                 const float2 uc = *reinterpret_cast<const float2 *>(&sU[col]);
@@ -587,6 +593,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
                     loc[4 * nn + 2 + e] += pb;
                     if (r0 == 0) sXtot[w4 * 64 + col + e] = pa;
                 }
+                if (nn < 3) tmem_wait_ld();
             }
             {   // block totals of b: 8 channel sums over the 8 lanes that share q, in 7 shuffles; lane r0 ends with channel
                 // value index e = 4*bit4 + 2*bit3 + bit2 of its lane number
