@@ -129,6 +129,36 @@ def test_backward_vs_oracle(pkg, B, T, H, with_ckpt):
             assert scaled_err(got, want) <= TOL_BF16, f"{name}: {scaled_err(got, want):.3e}"
 
 
+@pytest.mark.parametrize("T", [160, 100])
+def test_head_sharded_view(pkg, T):
+    """Half of the heads as [B, T, C/2] views of [B, T, C] tensors (a row stride, as the head split over GPUs passes them):
+    equal to the oracle on that half, and bit-equal to a run on contiguous copies.  T = 160 takes the fast backward's
+    paired-token tensor maps, T = 100 its natural-order maps."""
+    B, H = 2, 4
+    d = O.make_inputs(B, T, H, N, seed=77 + T)
+    t = dev_inputs(d)
+    hs = slice(2 * N, 4 * N)
+    views = [t[n][..., hs] for n in ("r", "k", "v", "w")]
+    assert not views[0].is_contiguous()
+    u = t["u"][2:].contiguous()
+    y, _, ck = pkg.forward_raw(*views, u, N, want_ckpt=True, variant=pkg.VARIANT_CHUNK)
+    g = pkg.backward_raw(*views, u, t["gy"][..., hs], N, ckpt=ck, variant=pkg.VARIANT_CHUNK)
+    yc, _, ckc = pkg.forward_raw(*(x.contiguous() for x in views), u, N, want_ckpt=True, variant=pkg.VARIANT_CHUNK)
+    gc = pkg.backward_raw(*(x.contiguous() for x in views), u, t["gy"][..., hs].contiguous(), N, ckpt=ckc, variant=pkg.VARIANT_CHUNK)
+    torch.cuda.synchronize()
+    assert status(pkg) == 0
+    assert torch.equal(y, yc)
+    for a, b in zip(g, gc):
+        assert torch.equal(a, b)
+    dr = rounded(d, torch.bfloat16)
+    sub = {n: np.ascontiguousarray(dr[n][..., hs]) for n in ("r", "k", "v", "w", "gy")}
+    yo, _ = c_oracle.fwd(sub["r"], sub["k"], sub["v"], sub["w"], dr["u"][2:], N)
+    assert scaled_err(np_(y), yo) <= TOL_BF16
+    ref = c_oracle.bwd(sub["r"], sub["k"], sub["v"], sub["w"], dr["u"][2:], sub["gy"], N)
+    for name, got, want in zip(("gr", "gk", "gv", "gw", "gu"), g, ref):
+        assert scaled_err(np_(got), want) <= TOL_BF16, f"{name}: {scaled_err(np_(got), want):.3e}"
+
+
 def test_backward_extreme_decay(pkg):
     B, T, H = 1, 192, 2
     d = O.make_inputs(B, T, H, N, seed=41)
