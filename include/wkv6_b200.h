@@ -229,6 +229,10 @@ WKV6_API int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const vo
                                   const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu,
                                   const void *ckpt, const float *ab_in, void *workspace, size_t workspace_bytes,
                                   void *stream);
+/* out[j] = sum over the rows of in[rows][n] (fp32, rows added in ascending order): the per-segment gu rows of
+ * wkv6_backward_seeded summed into the [H, N] gradient of u (the reference sums its per-batch-row gu the same way,
+ * jax_rwkv_kernel.py:202).  One small launch. */
+WKV6_API int wkv6_sum_rows(const float *in, int64_t rows, int64_t n, float *out, void *stream);
 
 /*
  * Output stage of the time-mix block, fused: per-head normalisation of the WKV output, then the gate:

@@ -188,6 +188,14 @@ int wkv6_state_scan(int32_t B, int32_t H, int32_t N, int32_t G, const float *dec
     return chunk_state_scan(B, H, G, dec_log2, state_sum, s0, state_in_out, last_out, reverse != 0, static_cast<cudaStream_t>(stream));
 }
 
+int wkv6_sum_rows(const float *in, int64_t rows, int64_t n, float *out, void *stream) {
+    if (rows < 0 || n < 0) return fail(WKV6_ERR_INVALID, "wkv6_sum_rows: rows=%lld n=%lld", (long long)rows, (long long)n);
+    if (n == 0) return WKV6_OK;
+    if (in == nullptr && rows > 0) return fail(WKV6_ERR_INVALID, "wkv6_sum_rows: NULL input");
+    if (out == nullptr) return fail(WKV6_ERR_INVALID, "wkv6_sum_rows: NULL output");
+    return chunk_sum_rows(in, rows, n, out, static_cast<cudaStream_t>(stream));
+}
+
 int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w, const void *u,
                          const void *gy, void *gr, void *gk, void *gv, void *gw, void *gu, const void *ckpt,
                          const float *ab_in, void *workspace, size_t workspace_bytes, void *stream) {

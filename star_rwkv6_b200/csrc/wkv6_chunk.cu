@@ -208,11 +208,28 @@ __global__ void state_scan_kernel(int B, int H, int G, const float *__restrict__
     const int ij = (int)(idx & 4095), i = ij >> 6;
     const int h = (int)((idx >> 12) % H), b = (int)(idx / ((size_t)H * 4096));
     float s = (!reverse && s0 != nullptr) ? s0[idx] : 0.f;
-    for (int gg = 0; gg < G; ++gg) {
-        const int g = reverse ? G - 1 - gg : gg;
-        const size_t seq = ((size_t)(b * G + g) * H + h);
-        out[seq * 4096 + ij] = s;
-        s = fmaf(exp2f(dec[seq * 64 + i]), s, bsum[seq * 4096 + ij]);
+    // eight segments at a time: their loads do not depend on the running state, so they are all requested before the
+    // first of them is folded in (one memory round trip per eight segments instead of one per segment)
+    for (int g0 = 0; g0 < G; g0 += 8) {
+        float d8[8], b8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int gg = g0 + e;
+            if (gg < G) {
+                const size_t seq = ((size_t)(b * G + (reverse ? G - 1 - gg : gg)) * H + h);
+                d8[e] = dec[seq * 64 + i];
+                b8[e] = bsum[seq * 4096 + ij];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int gg = g0 + e;
+            if (gg < G) {
+                const size_t seq = ((size_t)(b * G + (reverse ? G - 1 - gg : gg)) * H + h);
+                out[seq * 4096 + ij] = s;
+                s = fmaf(exp2f(d8[e]), s, b8[e]);
+            }
+        }
     }
     if (last != nullptr) last[idx] = s;
 }
@@ -224,6 +241,28 @@ int chunk_state_scan(int B, int H, int G, const float *dec, const float *bsum, c
     state_scan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(B, H, G, dec, bsum, s0, out, last, reverse);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "state_scan_kernel launch");
+}
+
+__global__ void sum_rows_kernel(const float *__restrict__ in, long long rows, long long n, float *__restrict__ out) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    float s = 0.f;
+    long long r0 = 0;
+    for (; r0 + 8 <= rows; r0 += 8) {  // eight independent loads in flight, added in row order
+        float v8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v8[e] = in[(r0 + e) * n + j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += v8[e];
+    }
+    for (; r0 < rows; ++r0) s += in[r0 * n + j];
+    out[j] = s;
+}
+
+int chunk_sum_rows(const float *in, int64_t rows, int64_t n, float *out, cudaStream_t st) {
+    sum_rows_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(in, rows, n, out);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "sum_rows_kernel launch");
 }
 
 // Read and clear: the word reports what happened since the previous query.  (cudaMemcpyFromSymbol synchronises.)

@@ -35,6 +35,7 @@ bool chunk_supported(const wkv6_problem *p);
 int chunk_status();
 int chunk_debug_inject(int skip_load_chunk, long long wait_limit_ms);
 size_t chunk_ckpt_bytes(const wkv6_problem *p);
+int chunk_sum_rows(const float *in, int64_t rows, int64_t n, float *out, cudaStream_t st);
 size_t chunk_backward_workspace(const wkv6_problem *p, const Dims &d, int have_ckpt);
 int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const void *k, const void *v, const void *w,
                   const void *u, void *y, const void *s_in, const int64_t *s_map, int s_kinds, void *s_out,

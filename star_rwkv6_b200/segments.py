@@ -103,6 +103,16 @@ class LibraryBackend:
         return (*g, gu)
 
 
+    def sum_rows(self, rows: torch.Tensor) -> torch.Tensor:
+        """[R, H, N] fp32 -> [H, N]: the per-segment gu rows added up (one small launch)."""
+        rows = rows.contiguous()
+        out = self._buf("gu_sum", tuple(rows.shape[1:]), torch.float32, rows.device)
+        n = out.numel()
+        with torch.cuda.device(rows.device):
+            self.L.check(self.L.lib.wkv6_sum_rows(self.ops._ptr(rows), rows.shape[0], n, self.ops._ptr(out), self._stream(rows)))
+        return out
+
+
 def auto_segments(B: int, T: int, H: int, target_sequences: int = 256, max_segments: int = 16, min_tokens: int = 256) -> int:
     """Number of segments that brings B*H*G independent sequences to about two per SM (the kernels run two CTAs per
     SM, one CTA per sequence): a power of two, dividing T, with at least ``min_tokens`` tokens per segment."""
@@ -166,7 +176,7 @@ def segmented_backward(backend, ctx, r, k, v, w, u, gy):
     a_in_all, _ = backend.scan(B, H, R * G, ctx["dec_all"], astate_all, None, True)
     a_in = _local_segments(a_in_all, B, G, group)
     gr, gk, gv, gw, gu_rows = backend.backward(rs, ks, vs, ws, u, gs, ctx["ckpt"], a_in)
-    gu = gu_rows.sum(0)
+    gu = backend.sum_rows(gu_rows) if hasattr(backend, "sum_rows") else gu_rows.sum(0)
     if R > 1:
         dist.all_reduce(gu, op=dist.ReduceOp.SUM, group=group)
     return gr.view(B, T, C), gk.view(B, T, C), gv.view(B, T, C), gw.view(B, T, C), gu

@@ -224,6 +224,20 @@ def test_backward_bit_identical_reruns(pkg):
         assert torch.equal(x, y)
 
 
+@pytest.mark.parametrize("rows,n", [(8, 2048), (19, 100), (1, 64), (0, 64)])
+def test_sum_rows(pkg, rows, n):
+    """wkv6_sum_rows (the gu rows of the segments added up) against a float64 sum."""
+    import ctypes
+    from star_rwkv6_b200 import _lib, ops
+    x = torch.randn(rows, n, device="cuda")
+    out = torch.full((n,), 7.0, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(_lib.lib.wkv6_sum_rows(ops._ptr(x) if rows else None, rows, n, ops._ptr(out), st))
+    torch.cuda.synchronize()
+    want = x.double().sum(0)
+    assert (out.double() - want).abs().max().item() <= 1e-5 * max(1.0, want.abs().max().item())
+
+
 @pytest.mark.parametrize("B,T,H,G", [(1, 512, 2, 2), (2, 1024, 2, 4), (1, 2048, 1, 8)])
 def test_segmented_matches_unsplit(pkg, B, T, H, G):
     """Sequences cut into G segments along T (summaries -> scan -> seeded kernels) against the one-piece kernels."""
