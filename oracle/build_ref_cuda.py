@@ -1,8 +1,8 @@
 """Compile the reference's own CUDA kernels for sm_100a into oracle/_ref/libref_wkv6_cuda.so.
 
 Test / benchmark infrastructure only: the product never loads this library.  The source is the reference's
-rwkv_kernel/jax_kernel/rwkv_kernels.cu, compiled where it lies in the reference tree (``WKV6_REFERENCE_DIR``, default
-/root/reference) with the reference's own flags (jax_rwkv_kernel.py:472-474: -O3 -DNDEBUG --expt-relaxed-constexpr,
+rwkv_kernel/jax_kernel/rwkv_kernels.cu, compiled where it lies in the reference tree (the directory ``WKV6_REFERENCE_DIR`` names)
+with the reference's own flags (jax_rwkv_kernel.py:472-474: -O3 -DNDEBUG --expt-relaxed-constexpr,
 hidden visibility, -D_N_ / -D_T_) except for the target architecture, plus the shim oracle/ref_cuda_shim.cu that gives
 its three handlers C names.  _N_ = 64 and _T_ = 4096 fix the head size and the longest sequence, as in the reference.
 Where the reference tree is absent (a GPU box) the prebuilt library is used as it is; build() then returns None when

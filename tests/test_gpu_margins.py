@@ -4,7 +4,7 @@ against the C oracle, scaled by the largest reference value, and the raw largest
 Cases: the fp32 smoke configuration (sequential kernels), the headline configuration B8 T4096 H32 in bf16 (chunked
 kernels; three sampled (batch, head) sequences, each at full length), the 131072-token sequence cut into segments
 (two sampled heads), and inputs that force the per-block reference points of the chunked kernels.  The test asserts
-the tolerances and writes the table to ``gpurun_out/parity_margins.md`` (the committed copy lives under
+the tolerances and writes the table as ``parity_margins.md`` into the run's output folder (the committed copy lives under
 ``profiles/``), so that a kernel change that spends error budget shows up as a number.
 """
 import os
