@@ -344,7 +344,8 @@ def run_b200(a):
         launches_per_step = 8  # forward: summary, scan, kernel; backward: summary, scan, fast + general kernel, gu row sum
 
         def step(d):
-            y, _, ctx = seg.segmented_forward(be, d["r"], d["k"], d["v"], d["w"], u, a.segments, want_ckpt=True, group=grp)
+            y, _, ctx = seg.segmented_forward(be, d["r"], d["k"], d["v"], d["w"], u, a.segments, want_ckpt=True, group=grp,
+                                              need_last=False)  # the step returns y and the gradients, not the final state
             return y, ctx
 
         def step_bwd(d, ctx):

@@ -223,6 +223,14 @@ WKV6_API int wkv6_softmax_xent_bf16(int64_t rows, int32_t V, void *logits_inout,
  */
 WKV6_API int wkv6_segment_summary(const wkv6_problem *p, const void *x1, const void *x2, const void *w, int reverse,
                                   float *state_out, float *dec_log2_out, void *stream);
+/* The same for a caller that only needs the states ENTERING the segments (an exclusive scan that does not return the
+ * state after the last segment): the problem holds G segments per sequence (p->B = sequences * G, segment g of sequence s
+ * at batch row s*G + g), and the one segment per sequence whose summary such a scan never reads is left out - the last
+ * one when reverse = 0, the first when reverse = 1.  Its rows of state_out and dec_log2_out are not written.  With
+ * reverse = 1 dec_log2_out holds exactly the decays the descending scan needs, so the backward no longer depends on the
+ * forward's summary. */
+WKV6_API int wkv6_segment_summary_for_scan(const wkv6_problem *p, const void *x1, const void *x2, const void *w, int reverse,
+                                           int32_t G, float *state_out, float *dec_log2_out, void *stream);
 WKV6_API int wkv6_state_scan(int32_t B, int32_t H, int32_t N, int32_t G, const float *dec_log2, const float *state_sum,
                              const float *s0, float *state_in_out, float *last_out, int reverse, void *stream);
 WKV6_API int wkv6_backward_seeded(const wkv6_problem *p, const void *r, const void *k, const void *v, const void *w,

@@ -21,7 +21,7 @@ SYMBOLS = (
     "wkv6_last_error", "wkv6_version", "wkv6_device_status", "wkv6_debug_inject", "wkv6_resolve_variant", "wkv6_forward", "wkv6_ckpt_bytes",
     "wkv6_backward", "wkv6_backward_workspace_bytes", "wkv6_backward_static_scratch", "wkv6_static_scratch_bytes",
     "wkv6_decode", "wkv6_decode_gated", "wkv6_decode_ln_shift_mix", "wkv6_decode_lora_mix", "wkv6_decode_relu_sq",
-    "wkv6_decode_sigmoid_mul_add", "wkv6_softmax_xent_bf16", "wkv6_segment_summary", "wkv6_state_scan", "wkv6_backward_seeded", "wkv6_sum_rows",
+    "wkv6_decode_sigmoid_mul_add", "wkv6_softmax_xent_bf16", "wkv6_segment_summary", "wkv6_segment_summary_for_scan", "wkv6_state_scan", "wkv6_backward_seeded", "wkv6_sum_rows",
     "wkv6_groupnorm_gate_forward", "wkv6_groupnorm_gate_backward", "wkv6_groupnorm_gate_workspace_bytes",
     "wkv6_groupnorm_silu_gate_forward", "wkv6_groupnorm_silu_gate_backward",
     "wkv6_shift_mix_forward", "wkv6_shift_mix_backward", "wkv6_shift_mix_workspace_bytes", "wkv6_copy_2d_async",
@@ -92,6 +92,8 @@ def _load():
     lib.wkv6_softmax_xent_bf16.argtypes = [ctypes.c_int64, i32, vp, i64p, ctypes.c_float, vp, vp]
     lib.wkv6_segment_summary.restype = ctypes.c_int
     lib.wkv6_segment_summary.argtypes = [pp, vp, vp, vp, ctypes.c_int, vp, vp, vp]
+    lib.wkv6_segment_summary_for_scan.restype = ctypes.c_int
+    lib.wkv6_segment_summary_for_scan.argtypes = [pp, vp, vp, vp, ctypes.c_int, i32, vp, vp, vp]
     lib.wkv6_sum_rows.restype = ctypes.c_int
     lib.wkv6_sum_rows.argtypes = [vp, ctypes.c_int64, ctypes.c_int64, vp, vp]
     lib.wkv6_state_scan.restype = ctypes.c_int

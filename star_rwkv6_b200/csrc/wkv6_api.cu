@@ -177,7 +177,20 @@ int wkv6_segment_summary(const wkv6_problem *p, const void *x1, const void *x2, 
     if (!chunk_supported(p)) return fail(WKV6_ERR_UNSUPPORTED, "segment summaries need the chunked variant (N == 64, bf16)");
     if (p->B == 0 || p->H == 0) return WKV6_OK;
     WKV6_CHECK_PTR(x1); WKV6_CHECK_PTR(x2); WKV6_CHECK_PTR(w); WKV6_CHECK_PTR(state_out); WKV6_CHECK_PTR(dec_log2_out);
-    return chunk_segment_summary(p, d, x1, x2, w, reverse != 0, state_out, dec_log2_out, static_cast<cudaStream_t>(stream));
+    return chunk_segment_summary(p, d, x1, x2, w, reverse != 0, state_out, dec_log2_out, 0, 0, static_cast<cudaStream_t>(stream));
+}
+
+int wkv6_segment_summary_for_scan(const wkv6_problem *p, const void *x1, const void *x2, const void *w, int reverse, int32_t G,
+                                  float *state_out, float *dec_log2_out, void *stream) {
+    Dims d;
+    int rc = validate(p, &d);
+    if (rc) return rc;
+    if (!chunk_supported(p)) return fail(WKV6_ERR_UNSUPPORTED, "segment summaries need the chunked variant (N == 64, bf16)");
+    if (G < 1 || p->B % G != 0) return fail(WKV6_ERR_INVALID, "wkv6_segment_summary_for_scan: B=%d is not a multiple of G=%d", p->B, G);
+    if (p->B == 0 || p->H == 0) return WKV6_OK;
+    WKV6_CHECK_PTR(x1); WKV6_CHECK_PTR(x2); WKV6_CHECK_PTR(w); WKV6_CHECK_PTR(state_out); WKV6_CHECK_PTR(dec_log2_out);
+    return chunk_segment_summary(p, d, x1, x2, w, reverse != 0, state_out, dec_log2_out, G, reverse ? 0 : G - 1,
+                                 static_cast<cudaStream_t>(stream));
 }
 
 int wkv6_state_scan(int32_t B, int32_t H, int32_t N, int32_t G, const float *dec_log2, const float *state_sum,

@@ -179,7 +179,7 @@ int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, c
 // the sequence builds from zero.  Forward direction: x1 = k, x2 = v.  Reverse direction (the backward's state):
 // x1 = r, x2 = gy.  A kernel of its own (wkv6_chunk_summary.cuh): one scaled operand and one product per chunk.
 int chunk_segment_summary(const wkv6_problem *p, const Dims &d, const void *x1, const void *x2, const void *w,
-                          bool reverse, float *b_out, float *dec_log2_out, cudaStream_t st) {
+                          bool reverse, float *b_out, float *dec_log2_out, int skip_mod, int skip_rem, cudaStream_t st) {
     CUtensorMap m1, m2, mw;
     int rc;
     if ((rc = make_map(&m1, x1, p, d, "x1"))) return rc;
@@ -188,6 +188,7 @@ int chunk_segment_summary(const wkv6_problem *p, const Dims &d, const void *x1, 
     ChunkFwdArgs a{};
     a.u = nullptr; a.u_dtype = WKV6_F32; a.s_dtype = WKV6_F32; a.s_out = b_out; a.B = p->B; a.T = p->T; a.H = p->H;
     a.write_y = false; a.reverse_state = reverse; a.dec_out = dec_log2_out;
+    a.skip_mod = skip_mod; a.skip_rem = skip_rem;
     cudaError_t e = cudaFuncSetAttribute(chunk_summary_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ChunkSumSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_summary_kernel)");

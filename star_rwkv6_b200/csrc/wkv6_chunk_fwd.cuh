@@ -86,6 +86,7 @@ struct ChunkFwdArgs {
     // reverse state of the backward (x1 = r, x2 = gy); and where to leave log2 of the total decay per key channel.
     bool reverse_state;
     float *dec_out;       // optional [B*H][64]
+    int skip_mod, skip_rem;  // summary kernel: sequences (batch rows) with b % skip_mod == skip_rem are left out (0: none)
 };
 
 __device__ __forceinline__ float ex2f(float x) {

@@ -37,6 +37,8 @@ __global__ void __launch_bounds__(256, 2) chunk_summary_kernel(const __grid_cons
         if (threadIdx.x == 0) atomicExch(&g_chunk_status, 50);
         return;
     }
+    // a segment whose summary the caller's scan never reads (the last of a sequence going forward, the first in reverse)
+    if (a.skip_mod > 0 && (int)(blockIdx.x / a.H) % a.skip_mod == a.skip_rem) return;
     float *sHead = reinterpret_cast<float *>(smem + SM::oHead);
     float *sTail = reinterpret_cast<float *>(smem + SM::oTail);
     float *sDtot = reinterpret_cast<float *>(smem + SM::oDtot);

@@ -48,7 +48,7 @@ int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, c
                           const void *w, const void *u, const void *gy, void *gr, void *gk, void *gv, void *gw,
                           void *gu, const void *ckpt, const float *ab_in, void *ws, size_t ws_bytes, cudaStream_t st);
 int chunk_segment_summary(const wkv6_problem *p, const Dims &d, const void *x1, const void *x2, const void *w,
-                          bool reverse, float *b_out, float *dec_log2_out, cudaStream_t st);
+                          bool reverse, float *b_out, float *dec_log2_out, int skip_mod, int skip_rem, cudaStream_t st);
 int chunk_state_scan(int B, int H, int G, const float *dec, const float *bsum, const float *s0, float *out, float *last,
                      bool reverse, cudaStream_t st);
 int resolve_variant(const wkv6_problem *p);

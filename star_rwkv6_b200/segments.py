@@ -32,6 +32,7 @@ class LibraryBackend:
         self.L, self.ops, self.N = _lib, ops, head_size
         self.reuse = reuse_buffers
         self._bufs = {}
+        self.scan_only_summaries = True   # summary() accepts scan_only_segments
 
     def _buf(self, name, shape, dtype, device):
         if not self.reuse:
@@ -49,7 +50,9 @@ class LibraryBackend:
     def _stream(self, x):
         return ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
 
-    def summary(self, x1, x2, w, reverse: bool):
+    def summary(self, x1, x2, w, reverse: bool, scan_only_segments: int = 0):
+        """Summaries of the rows of [B*G, Tseg, C] tensors.  ``scan_only_segments`` = G > 0: leave out the one segment per
+        sequence that an exclusive scan never reads (see wkv6_segment_summary_for_scan); its rows come back unwritten."""
         Bn, T, C = x1.shape
         H = C // self.N
         tag = "rev" if reverse else "fwd"
@@ -58,8 +61,12 @@ class LibraryBackend:
         p = self._problem(x1)
         ptr = self.ops._ptr
         with torch.cuda.device(x1.device):
-            self.L.check(self.L.lib.wkv6_segment_summary(ctypes.byref(p), ptr(x1), ptr(x2), ptr(w), int(reverse), ptr(state),
-                                                         ptr(dec), self._stream(x1)))
+            if scan_only_segments > 0:
+                self.L.check(self.L.lib.wkv6_segment_summary_for_scan(ctypes.byref(p), ptr(x1), ptr(x2), ptr(w), int(reverse),
+                                                                      scan_only_segments, ptr(state), ptr(dec), self._stream(x1)))
+            else:
+                self.L.check(self.L.lib.wkv6_segment_summary(ctypes.byref(p), ptr(x1), ptr(x2), ptr(w), int(reverse), ptr(state),
+                                                             ptr(dec), self._stream(x1)))
         return state, dec
 
     def scan(self, B, H, G, dec, state, s0, reverse: bool):
@@ -149,20 +156,24 @@ def _local_segments(x: torch.Tensor, B: int, G: int, group) -> torch.Tensor:
 
 
 def segmented_forward(backend, r, k, v, w, u, segments: int, init_state: Optional[torch.Tensor] = None,
-                      want_ckpt: bool = False, group=None):
-    """Forward over local tensors [B, T_local, C].  Returns (y, state after the whole sequence, context for backward)."""
+                      want_ckpt: bool = False, group=None, need_last: bool = True):
+    """Forward over local tensors [B, T_local, C].  Returns (y, state after the whole sequence, context for backward).
+
+    ``need_last=False`` (one rank only): the caller does not want the final state, so the summary of every sequence's last
+    segment - and, in the backward, of its first - is not computed (None comes back in place of the state)."""
     B, T, C = r.shape
     G = segments
     rs, ks, vs, ws = (_split(x, G) for x in (r, k, v, w))
-    state, dec = backend.summary(ks, vs, ws, False)
-    H = state.shape[1]
     R = 1 if group is None else dist.get_world_size(group)
+    lean = (not need_last) and R == 1 and getattr(backend, "scan_only_summaries", False)
+    state, dec = backend.summary(ks, vs, ws, False, G) if lean else backend.summary(ks, vs, ws, False)
+    H = state.shape[1]
     state_all, dec_all = _gather_segments(state, B, G, group), _gather_segments(dec, B, G, group)
     s_in_all, last = backend.scan(B, H, R * G, dec_all, state_all, init_state, False)
     s_in = _local_segments(s_in_all, B, G, group)
     y, ckpt = backend.forward(rs, ks, vs, ws, u, s_in, want_ckpt)
-    ctx = dict(dec_all=dec_all, ckpt=ckpt, B=B, G=G, H=H, group=group)
-    return y.view(B, T, C), last, ctx
+    ctx = dict(dec_all=dec_all, ckpt=ckpt, B=B, G=G, H=H, group=group, lean=lean)
+    return y.view(B, T, C), (None if lean else last), ctx
 
 
 def segmented_backward(backend, ctx, r, k, v, w, u, gy):
@@ -170,10 +181,14 @@ def segmented_backward(backend, ctx, r, k, v, w, u, gy):
     B, G, H, group = ctx["B"], ctx["G"], ctx["H"], ctx["group"]
     T, C = r.shape[1], r.shape[2]
     rs, ks, vs, ws, gs = (_split(x, G) for x in (r, k, v, w, gy))
-    astate, _ = backend.summary(rs, gs, ws, True)
     R = 1 if group is None else dist.get_world_size(group)
+    if ctx.get("lean"):  # the reverse summaries bring the decays their scan needs (the forward left out the last segment's)
+        astate, dec_all = backend.summary(rs, gs, ws, True, G)
+    else:
+        astate, _ = backend.summary(rs, gs, ws, True)
+        dec_all = ctx["dec_all"]
     astate_all = _gather_segments(astate, B, G, group)
-    a_in_all, _ = backend.scan(B, H, R * G, ctx["dec_all"], astate_all, None, True)
+    a_in_all, _ = backend.scan(B, H, R * G, dec_all, astate_all, None, True)
     a_in = _local_segments(a_in_all, B, G, group)
     gr, gk, gv, gw, gu_rows = backend.backward(rs, ks, vs, ws, u, gs, ctx["ckpt"], a_in)
     gu = backend.sum_rows(gu_rows) if hasattr(backend, "sum_rows") else gu_rows.sum(0)
@@ -185,7 +200,7 @@ def segmented_backward(backend, ctx, r, k, v, w, u, gy):
 class _SegmentedWKV6(torch.autograd.Function):
     @staticmethod
     def forward(ctx, r, k, v, w, u, backend, segments, group):
-        y, _, c = segmented_forward(backend, r, k, v, w, u, segments, want_ckpt=True, group=group)
+        y, _, c = segmented_forward(backend, r, k, v, w, u, segments, want_ckpt=True, group=group, need_last=False)
         ctx.save_for_backward(r, k, v, w, u)
         ctx.c, ctx.backend = c, backend
         return y

@@ -263,6 +263,30 @@ def test_segmented_matches_unsplit(pkg, B, T, H, G):
     assert scaled_err(np_(last), np_(s1)) <= 1e-2   # two bf16 roundings of the operands apart (summary kernel / forward kernel)
 
 
+@pytest.mark.parametrize("B,T,H,G", [(2, 512, 2, 2), (1, 2048, 2, 8)])
+def test_segmented_without_final_state(pkg, B, T, H, G):
+    """need_last=False leaves out the summaries no scan reads (last segment forward, first in reverse): the results are
+    bit-equal to the full run, whatever the unwritten summary rows hold (they are poisoned with NaN here)."""
+    from star_rwkv6_b200 import segments as seg
+    d = O.make_inputs(B, T, H, N, seed=85 + G)
+    t = dev_inputs(d)
+    full = seg.LibraryBackend(N)
+    y0, last, ctx0 = seg.segmented_forward(full, t["r"], t["k"], t["v"], t["w"], t["u"], G, want_ckpt=True)
+    g0 = seg.segmented_backward(full, ctx0, t["r"], t["k"], t["v"], t["w"], t["u"], t["gy"])
+    lean = seg.LibraryBackend(N, reuse_buffers=True)
+    for tag in ("fwd", "rev"):   # the buffers the lean run will reuse, filled with NaN beforehand
+        lean._buf("sum_state_" + tag, (B * G, H, N, N), torch.float32, t["r"].device).fill_(float("nan"))
+        lean._buf("sum_dec_" + tag, (B * G, H, N), torch.float32, t["r"].device).fill_(float("nan"))
+    y1, none, ctx1 = seg.segmented_forward(lean, t["r"], t["k"], t["v"], t["w"], t["u"], G, want_ckpt=True, need_last=False)
+    g1 = seg.segmented_backward(lean, ctx1, t["r"], t["k"], t["v"], t["w"], t["u"], t["gy"])
+    torch.cuda.synchronize()
+    assert status(pkg) == 0 and none is None and ctx1["lean"]
+    assert torch.equal(y0, y1)
+    for a, b in zip(g0[:4], g1[:4]):
+        assert torch.equal(a, b)
+    assert scaled_err(np_(g1[4]), np_(g0[4])) <= 1e-6
+
+
 def test_segmented_autograd(pkg):
     from star_rwkv6_b200 import segments as seg
     d = O.make_inputs(1, 1024, 2, N, seed=91)
