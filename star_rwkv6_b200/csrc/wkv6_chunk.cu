@@ -1,4 +1,5 @@
 // Host side of the chunked tensor-core variant: TMA descriptors, launches, workspace sizes.
+#include <atomic>
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -9,6 +10,9 @@
 #include "wkv6_internal.h"
 
 namespace wkv6 {
+
+// Test hook (wkv6_debug_inject): chunk index whose input tiles the forward never requests, -1 = off.
+static std::atomic<int> g_skip_load_chunk{-1};
 
 static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = []() -> PFN_cuTensorMapEncodeTiled_v12000 {
@@ -93,6 +97,7 @@ int chunk_forward(const wkv6_problem *p, const Dims &d, const void *r, const voi
     a.u = u; a.u_dtype = p->u_dtype; a.s_in = s_in; a.s_map = s_map; a.s_kinds = s_kinds; a.s_dtype = p->s_dtype;
     a.s_out = s_out; a.write_y = (y != nullptr); a.ckpt = static_cast<__nv_bfloat16 *>(ckpt);
     a.reverse_state = false; a.dec_out = nullptr; a.B = p->B; a.T = p->T; a.H = p->H;
+    a.skip_load_chunk = g_skip_load_chunk.load() + 1;
     cudaError_t e = cudaFuncSetAttribute(chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ChunkFwdSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_fwd_kernel)");
@@ -281,7 +286,7 @@ int chunk_status() {
 int chunk_debug_inject(int skip_load_chunk, long long wait_limit_ms) {
     const unsigned long long ns = wait_limit_ms > 0 ? (unsigned long long)wait_limit_ms * 1000000ull : 1000000000ull;
     cudaError_t e = cudaMemcpyToSymbol(ptx::g_wait_limit_ns, &ns, sizeof(ns));
-    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_skip_load_chunk, &skip_load_chunk, sizeof(int));
+    g_skip_load_chunk.store(skip_load_chunk);  // travels to the forward kernel as an argument of its next launches
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "cudaMemcpyToSymbol(debug hooks)");
 }
 
@@ -290,5 +295,8 @@ int chunk_debug_inject(int skip_load_chunk, long long wait_limit_ms) {
 #ifdef WKV6_TIMING
 extern "C" __attribute__((visibility("default"))) int wkv6_debug_timing(long long *out) {
     return (int)cudaMemcpyFromSymbol(out, wkv6::g_chunk_timing, sizeof(long long) * 64 * 16 * 8);
+}
+extern "C" __attribute__((visibility("default"))) int wkv6_debug_cta_times(long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, wkv6::g_cta_times, sizeof(long long) * 1024 * 8);
 }
 #endif

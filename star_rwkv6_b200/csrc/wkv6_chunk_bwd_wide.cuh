@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     const int ta = 16 * w4 + r0;  // this thread's rows: ta and ta + 8
     const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
     const int nchunks = (a.T + kChunk - 1) / kChunk;
+    WKV6_CSTAMP(0);
 
     if (tid == 0) {
         mbar_init(bar_w, 1);
@@ -148,6 +149,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    WKV6_CSTAMP(1);
     const uint32_t tbase = *slot;
     const uint32_t lo = (uint32_t)(32 * w4) << 16;  // this warp's TMEM lane quarter
     const uint32_t tmP = tbase, tmA = tbase + 64, tmGR2 = tbase + 128, tmGK2 = tbase + 192;
@@ -212,10 +214,12 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         tmem_st_16x256b_x2(tmGUp, z8);
         tmem_wait_st();
     }
+    WKV6_CSTAMP(2);
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    WKV6_CSTAMP(3);
 
 
     constexpr uint32_t idKK = umma_idesc_bf16(64, 64, false, false);
@@ -236,6 +240,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         if (!cta_wait(bar_w, it & 1, warp)) err = 1;
         if (copy_thread) pend_w = false;
         WKV6_TSTAMP(it, 1);
+        if (it == 0) WKV6_CSTAMP(4);
 
         // ---- per-step log2 decays and their running sums inside the block (fragment layout)
         __nv_bfloat162 ekb[8];  // e^{ref-c_t} rounded to bf16: index 2*nn + (row ta+8 ? 1 : 0)
@@ -678,6 +683,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         }
     }
 
+    WKV6_CSTAMP(5);
     // ---- unwind: wait (bounded) for loads still aimed at this CTA's shared memory, drain the stores, report
     if (copy_thread) {
         if (err != 0 || bail) {
@@ -689,6 +695,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         bulk_wait<0>();
         a.flags[blockIdx.x] = (bail && err == 0) ? 1 : 0;
     }
+    __syncthreads();
+    WKV6_CSTAMP(6);
     // gu[b][h][i]: sum this thread's channels over the 8 lanes sharing q, then over the four row blocks
     float gu_acc[8];
     tmem_ld_16x256b_x2(tmGUp, gu_acc);
@@ -713,6 +721,7 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     if (tid < 64 && err == 0 && !bail)
         store_any(a.gu, a.gu_dtype, (size_t)blockIdx.x * 64 + tid, sGU[tid] + sGU[64 + tid] + sGU[128 + tid] + sGU[192 + tid]);
     if (warp == 0) tmem_dealloc(tbase, 256);
+    WKV6_CSTAMP(7);
 }
 
 }  // namespace wkv6

@@ -45,17 +45,17 @@ constexpr float kWideLimit2 = -96.0f;
 
 // device-side error word: 0 = fine, otherwise the code of the wait that ran out (read and cleared by the host)
 __device__ int g_chunk_status;
-// Test hook (wkv6_debug_inject): the forward never requests the input tiles of this chunk index (-1 = off), so the
-// wait for them runs out with no copy outstanding and the kernel takes its error path.
-__device__ int g_skip_load_chunk = -1;
 
 // Phase timestamps of CTA 0 (builds with -DWKV6_TIMING only): g_chunk_timing[chunk][phase][warp] = clock64() of lane 0
 #ifdef WKV6_TIMING
 __device__ long long g_chunk_timing[64][16][8];
+__device__ long long g_cta_times[1024][8];  // per CTA: four globaltimer stamps (entry, loop start, loop end, exit)
+#define WKV6_CSTAMP(k) do { if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta_times[blockIdx.x][(k)] = (long long)ptx::global_timer_ns(); } while (0)
 #define WKV6_TSTAMP(iter, k) \
     do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (iter) < 64) g_chunk_timing[(iter)][(k)][threadIdx.x >> 5] = clock64(); } while (0)
 #else
 #define WKV6_TSTAMP(iter, k) do { } while (0)
+#define WKV6_CSTAMP(k) do { } while (0)
 #endif
 
 struct ChunkFwdSmem {
@@ -87,6 +87,9 @@ struct ChunkFwdArgs {
     bool reverse_state;
     float *dec_out;       // optional [B*H][64]
     int skip_mod, skip_rem;  // summary kernel: sequences (batch rows) with b % skip_mod == skip_rem are left out (0: none)
+    // Test hook (wkv6_debug_inject): the forward never requests the input tiles of chunk index skip_load_chunk - 1
+    // (0 = off), so the wait for them runs out with no copy outstanding and the kernel takes its error path.
+    int skip_load_chunk;
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -170,6 +173,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     const int ta = 16 * w4 + r0;
     const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
     const int nchunks = (a.T + kChunk - 1) / kChunk;
+    WKV6_CSTAMP(0);
 
     if (tid == 0) {
         mbar_init(&bar_full[0], 4);  // one arrival per loading thread
@@ -186,11 +190,12 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     }
 
     __syncthreads();  // the barriers are initialised: the first two chunks can be requested before the state is read
+    WKV6_CSTAMP(1);
     // Issuing a TMA copy keeps a thread busy for on the order of a hundred cycles, so the copies of one chunk are
     // spread over warps: lane 0 of warps 2..5 loads one input tile each, lane 0 of warp 1 issues the stores.  Warp 0,
     // whose first lane issues MMAs, issues none.
     const int load_slot = (lane == 0 && warp >= 2 && warp <= 5) ? warp - 2 : -1;  // 0..3 = r, k, v, w
-    const int skip_chunk = *reinterpret_cast<volatile int *>(&g_skip_load_chunk);  // test hook, -1 in normal use
+    const int skip_chunk = a.skip_load_chunk - 1;  // test hook, -1 in normal use
     auto issue_loads = [&](int ic2) {  // every thread calls it; the four loading threads act
         if (load_slot < 0 || ic2 == skip_chunk) return;
         const int c = ic2;
@@ -203,6 +208,12 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     issue_loads(0);
     if (nchunks > 1) issue_loads(1);
 
+    // u of this thread's channel pair (requested before the state so that the two reads overlap)
+    float2 u2 = make_float2(0.f, 0.f);
+    if (a.u != nullptr) {
+        if (a.u_dtype == WKV6_F32) u2 = *reinterpret_cast<const float2 *>(static_cast<const float *>(a.u) + (size_t)h * 64 + 2 * lane);
+        else u2 = make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane), load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane + 1));
+    }
     // state in accumulator-fragment layout: rows i = ta (+8), columns j = 8(n0+nn) + 2q (+1)
     float S[16];
     {
@@ -213,29 +224,45 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
             kind = kind < 0 ? 0 : (kind >= a.s_kinds ? a.s_kinds - 1 : kind);
             so = ((size_t)kind * a.H + h) * 4096;
         }
+        if (has && a.s_dtype == WKV6_F32) {
+            // eight independent 8-byte loads per thread (the generic reader below switches on the dtype per element,
+            // which serialises its sixteen loads: 5 us of a launch over short sequences)
+            const float *sp = static_cast<const float *>(a.s_in) + so;
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int j = 8 * (n0 + nn) + 2 * q;
+                const float2 lo2 = *reinterpret_cast<const float2 *>(sp + (size_t)ta * 64 + j);
+                const float2 hi2 = *reinterpret_cast<const float2 *>(sp + (size_t)(ta + 8) * 64 + j);
+                S[4 * nn] = lo2.x; S[4 * nn + 1] = lo2.y; S[4 * nn + 2] = hi2.x; S[4 * nn + 3] = hi2.y;
+            }
+        } else {
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn) {
+                const int j = 8 * (n0 + nn) + 2 * q;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = ta + (e >= 2 ? 8 : 0);
+                    S[4 * nn + e] = has ? load_any(a.s_in, a.s_dtype, so + (size_t)i * 64 + j + (e & 1)) : 0.f;
+                }
+            }
+        }
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn) {
             const int j = 8 * (n0 + nn) + 2 * q;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = ta + (e >= 2 ? 8 : 0);
-                S[4 * nn + e] = has ? load_any(a.s_in, a.s_dtype, so + (size_t)i * 64 + j + (e & 1)) : 0.f;
-            }
             *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta, j)) = pack_bf2(S[4 * nn], S[4 * nn + 1]);
             *reinterpret_cast<uint32_t *>(sSB + sw128_off(ta + 8, j)) = pack_bf2(S[4 * nn + 2], S[4 * nn + 3]);
         }
     }
-    const float2 u2 = a.u == nullptr ? make_float2(0.f, 0.f)
-                                     : make_float2(load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane),
-                                                   load_any(a.u, a.u_dtype, (size_t)h * 64 + 2 * lane + 1));
 
     const __nv_bfloat162 ub = to_bf2(u2);
 
+    WKV6_CSTAMP(2);
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tb = *slot;
+    WKV6_CSTAMP(3);
     const uint32_t tmA0 = tb, tmY = tb + 64, tmS = tb + 128, tmAU = tb + 192, tmAD = tb + (16u << 16);
     const uint32_t wl = (uint32_t)(w4 * 32) << 16;  // this warp's TMEM lane quarter
     const uint32_t cb = 8 * n0;                     // first accumulator column of this thread's fragment
@@ -295,9 +322,11 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     };
     if (!cta_wait(&bar_full[0], 0, warp)) err = 1;
     if (err == 0) ++loads_consumed;
+    WKV6_CSTAMP(4);
     pass1(0);
     if (!__syncthreads_and(err == 0)) err = err ? err : 10;
 
+    WKV6_CSTAMP(5);
     for (int ic = 0; ic < nchunks && err == 0; ++ic) {
         const int c = ic;  // chunk processed in this iteration
         const int st = ic & 1;
@@ -596,6 +625,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         if (ic + 2 < nchunks) { issue_loads(ic + 2); ++loads_issued; }
     }
 
+    WKV6_CSTAMP(6);
     // ---- unwind: drain this CTA's copies, report, release tensor memory
     if (err != 0 && load_slot >= 0) {
         // loads still in flight target this CTA's shared memory: wait for them (bounded) before leaving
@@ -619,6 +649,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tb, 256);
+    WKV6_CSTAMP(7);
 }
 
 }  // namespace wkv6
