@@ -18,7 +18,7 @@
 // The exponentials are split around per-16-token-block reference points exactly as in the forward, so every
 // bf16 operand stays finite; block pairs (I, J) are separate MMAs whose output is restricted to the 16 rows of
 // one block with the disable-output-lane mask of tcgen05.mma.  A chunk whose total decay is mild in every channel
-// (kWideLimit2) uses one reference point, the middle of the chunk, for all four blocks: the block-pair factors are
+// (kWideLimit2) uses one reference, half of the chunk's total log2 decay, for all four blocks: the block-pair factors are
 // then 1, the copies are skipped and GR1 / GK1 are two plain MMAs.
 //
 // All element-wise work is done in the accumulator-fragment layout of tcgen05.ld.16x256b: a thread owns tokens
@@ -352,8 +352,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant
                 ref[J2] = rintf(base + sHead[J2 * 64 + i]);  // integer: block-pair factors become powers of two
                 if (J2 == J) mybase = base;
                 base += sTot[J2 * 64 + i];
-                if (J2 == 1) cmid = rintf(base);
             }
+            cmid = rintf(0.5f * base);  // the single reference: half of the chunk's total log2 decay
             wide = !__syncthreads_or(base < kWideLimit2);
             float myref = ref[0];
 #pragma unroll

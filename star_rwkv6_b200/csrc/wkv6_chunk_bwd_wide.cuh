@@ -1,4 +1,4 @@
-// Chunked WKV6 backward, fast kernel: every chunk uses one reference point (the middle of the chunk) for the
+// Chunked WKV6 backward, fast kernel: every chunk uses one reference (half of the chunk's total log2 decay) for the
 // decay exponents, which is valid while the total log2 decay of a chunk stays above kWideLimit2 in every channel
 // (see wkv6_chunk_fwd.cuh).  The mathematics and the thread <-> element mapping are those of chunk_bwd_kernel
 // (wkv6_chunk_bwd.cuh); what differs is where per-element state lives between the phases of a chunk, because with
@@ -285,8 +285,8 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
         if (!__syncthreads_and(err == 0)) { err = err ? err : 10; break; }
         WKV6_TSTAMP(it, 2);
 
-        // ---- per channel: the reference point (an integer in the log2 domain, the running sum at the middle of the
-        // chunk) and the factors that depend on it; one (block, channel) pair per thread
+        // ---- per channel: the reference (an integer in the log2 domain, half of the chunk's total decay) and the
+        // factors that depend on it; one (block, channel) pair per thread
         {
             const int J = tid >> 6, i = tid & 63;
             float base = 0.f, mybase = 0.f, ref = 0.f;
@@ -294,10 +294,10 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
             for (int J2 = 0; J2 < 4; ++J2) {
                 if (J2 == J) mybase = base;
                 base += sTot[J2 * 64 + i];
-                if (J2 == 1) ref = rintf(base);
             }
             // The factors are written whether or not the chunk fits the single reference point; the test itself rides on
             // the barrier that publishes them (one CTA barrier fewer per chunk), with a second barrier only when it trips.
+            ref = rintf(0.5f * base);  // half of the chunk's total log2 decay: both operands' largest factors are 2^{-base/2}
             const bool over = base < kWideLimit2;
             sOff[J * 64 + i] = ref - mybase;
             if (J == 0) {

@@ -18,7 +18,7 @@
 // bf16 resolution of anything it multiplies), so every factor stays below e^80.  The block-pair factor is
 // folded into extra copies of k~ (one per block distance 1..3), all multiplied by the same r~ in one MMA;
 // the epilogue picks, per block pair, the columns of the matching copy.  Chunks with a mild total decay (see
-// kWideLimit2; the usual case) use the middle of the chunk as the single reference point and skip the copies.
+// kWideLimit2; the usual case) use a single reference (half of the chunk's total decay) and skip the copies.
 //
 // Tensor-memory map (256 columns, M = 64 accumulators occupy 16 lanes of each 32-lane quarter):
 //   lanes  0-15: cols [0,64) A for distance 0 | [64,128) y | [128,192) k~^T V (state increment) | [192,256) q k~^T (bonus)
@@ -39,9 +39,14 @@ constexpr int kTile = 8192;  // one [64 x 64] bf16 tile
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMinLogDecay2 = -10.0f * 1.4426950408889634f;  // clamp of the per-step log2 decay
 // A chunk whose total log2 decay stays above this limit in every channel takes one reference point for the whole
-// chunk (its middle) instead of one per 16-token block: every factor stays below 2^96, and the copies of k~ / r~
-// for the block distances 1..3 are not needed.
-constexpr float kWideLimit2 = -96.0f;
+// chunk instead of one per 16-token block, and the copies of k~ / r~ for the block distances 1..3 are not needed.
+// The reference is not a token position but a value: half of the chunk's total log2 decay (rounded to an integer), so
+// that the largest factor of r (at the first token) and of k (at the last) are both 2^{-total/2} <= 2^96, finite in
+// bf16 whatever r and k hold and however the decay is distributed over the chunk.  A channel may then lose up to 2^-3
+// per token on average (exp(w) up to 2.08, w up to 0.73).  Products of two such factors occur only at masked
+// positions (a key after its query), where they may overflow to infinity: every mask is a select, never a
+// multiplication, so nothing of them is used.
+constexpr float kWideLimit2 = -192.0f;
 
 // device-side error word: 0 = fine, otherwise the code of the wait that ran out (read and cleared by the host)
 __device__ int g_chunk_status;
@@ -340,22 +345,22 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_kernel(const __grid_constant
         // running sums of the second half are already relative to it and those of the first half need only -head.
         // The scaling itself runs on packed bf16 pairs: r and k are exact bf16 inputs, factors are rounded to bf16.
         {
-            float2 pre = make_float2(0.f, 0.f), post = make_float2(0.f, 0.f), head, tail, mid;
-            head = tail = mid = make_float2(0.f, 0.f);
+            float2 pre = make_float2(0.f, 0.f), head, tail, all;
+            head = tail = all = make_float2(0.f, 0.f);
 #pragma unroll
             for (int J = 0; J < 4; ++J) {
                 const float2 hj = *reinterpret_cast<const float2 *>(&sHead[J * 64 + 2 * lane]);
                 const float2 tl = *reinterpret_cast<const float2 *>(&sTail[J * 64 + 2 * lane]);
                 const float2 tj = add2(hj, tl);
                 if (J < w4) pre = add2(pre, tj);
-                if (J > w4) post = add2(post, tj);
                 if (J == w4) { head = hj; tail = tl; }
-                if (J < 2) mid = add2(mid, tj);
+                // log2 decay of the whole chunk, summed in the same order by every thread: the reference below is rounded
+                // from it, and all warps must round the same bits
+                all = add2(all, tj);
             }
-            const float2 all = add2(add2(head, tail), add2(pre, post));  // log2 decay of the whole chunk
             wide = !__any_sync(0xffffffffu, fminf(all.x, all.y) < kWideLimit2);  // a warp sees all 64 channels
-            // reference point relative to the chunk start: the block's 8th token, or the chunk's 32nd
-            const float2 ref = wide ? mid : add2(pre, head);
+            // reference relative to the chunk start: the block's 8th token, or half of the chunk's total decay (an integer)
+            const float2 ref = wide ? make_float2(rintf(0.5f * all.x), rintf(0.5f * all.y)) : add2(pre, head);
             const float2 gstart = half ? add2(pre, head) : pre;  // running sum before this thread's first token
             const float2 nbase = make_float2(gstart.x - ref.x, gstart.y - ref.y);
             const __nv_bfloat162 fR = to_bf2(make_float2(ex2f(ref.x), ex2f(ref.y)));

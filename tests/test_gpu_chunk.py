@@ -175,8 +175,8 @@ def test_backward_extreme_decay(pkg):
 
 
 def _strong_decay_inputs(kind, B, T, H, seed):
-    """Inputs whose chunks take the per-block reference points (total log2 decay of a chunk below -96 in some channel),
-    the single reference point, or a mix of both inside one sequence."""
+    """Inputs whose chunks take the per-block reference points (total log2 decay of a chunk below -192 in some channel),
+    the single reference, or a mix of both inside one sequence."""
     d = O.make_inputs(B, T, H, N, seed=seed)
     rng = np.random.default_rng(seed)
     w = d["w"].reshape(B, T, H, N)
@@ -188,13 +188,24 @@ def _strong_decay_inputs(kind, B, T, H, seed):
     elif kind == "bursts":           # short clamped bursts at odd offsets, straddling block and chunk borders
         for t0 in range(5, T, 97):
             w[:, t0:t0 + 9, :, ::3] = 4.0
-    elif kind == "borderline":       # total decay of a chunk close to the switch-over limit
-        w[...] = np.log(96.0 / 64 / 1.4426950408889634) + rng.uniform(-0.05, 0.05, size=w.shape)
+    elif kind == "borderline":       # total decay of a chunk close to the switch-over limit (192 bits over 64 tokens)
+        w[...] = np.log(192.0 / 64 / 1.4426950408889634) + rng.uniform(-0.05, 0.05, size=w.shape)
+    elif kind == "steady_fast":      # single reference point with factors up to 2^85: products at masked positions overflow
+        w[..., ::4] = 0.6 + rng.uniform(-0.02, 0.02, size=w[..., ::4].shape)
+    elif kind == "front_loaded":     # the first half of every chunk decays by about 90 bits in some channels, the second mildly
+        for c0 in range(0, T, 64):
+            w[:, c0:c0 + 32, :, 1::5] = 0.66 + rng.uniform(-0.02, 0.02, size=w[:, c0:c0 + 32, :, 1::5].shape)
+    elif kind == "lopsided":         # 115 of a chunk's 137 bits fall on its first 24 tokens: single reference, far from the middle
+        for c0 in range(0, T, 64):
+            w[:, c0:c0 + 24, :, ::7] = 1.2
+    elif kind == "back_loaded":
+        for c0 in range(0, T, 64):
+            w[:, c0 + 32:c0 + 64, :, 2::5] = 0.66 + rng.uniform(-0.02, 0.02, size=w[:, c0 + 32:c0 + 64, :, 2::5].shape)
     d["w"] = w.reshape(B, T, H * N).astype(np.float32)
     return d
 
 
-@pytest.mark.parametrize("kind", ["some_channels", "alternating", "bursts", "borderline"])
+@pytest.mark.parametrize("kind", ["some_channels", "alternating", "bursts", "borderline", "steady_fast", "front_loaded", "back_loaded", "lopsided"])
 def test_reference_point_modes(pkg, kind):
     B, T, H = 2, 448, 2
     d = _strong_decay_inputs(kind, B, T, H, seed=51)

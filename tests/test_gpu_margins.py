@@ -83,7 +83,7 @@ def test_margins_table():
     del d, y, last, ctx, g
 
     # per-block reference points (strong decays) and the switch between the two modes
-    for kind in ("some_channels", "alternating", "bursts", "borderline"):
+    for kind in ("some_channels", "alternating", "bursts", "borderline", "steady_fast", "front_loaded", "back_loaded", "lopsided"):
         d = _strong_decay_inputs(kind, 2, 448, 2, seed=51)
         t = {n: torch.tensor(d[n]).to(torch.bfloat16).cuda() for n in ("r", "k", "v", "w", "gy")}
         u = torch.tensor(d["u"]).cuda()
