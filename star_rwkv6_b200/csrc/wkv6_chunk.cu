@@ -11,6 +11,19 @@
 
 namespace wkv6 {
 
+// SMs of the current device (looked up once per device).
+static int sm_count() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = cached[dev].load();
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev].store(n);
+    }
+    return n;
+}
+
 // Test hook (wkv6_debug_inject): chunk index whose input tiles the forward never requests, -1 = off.
 static std::atomic<int> g_skip_load_chunk{-1};
 
@@ -173,9 +186,10 @@ int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, c
         e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "chunk_bwd_wide_kernel launch");
     }
-    e = cudaFuncSetAttribute(chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ChunkBwdSmem::kAlloc);
+    auto general = (int64_t)p->B * p->H <= sm_count() ? chunk_bwd_kernel<1> : chunk_bwd_kernel<2>;
+    e = cudaFuncSetAttribute(general, cudaFuncAttributeMaxDynamicSharedMemorySize, ChunkBwdSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_kernel)");
-    chunk_bwd_kernel<<<p->B * p->H, 256, ChunkBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
+    general<<<p->B * p->H, 256, ChunkBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
     e = cudaGetLastError();
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_bwd_kernel launch");
 }

@@ -163,7 +163,11 @@ __device__ __forceinline__ void scan_suffix16_adj(float &a, float &b, int r0) {
     a = t;       // ... plus a and b
 }
 
-__global__ void __launch_bounds__(256, 2) chunk_bwd_kernel(const __grid_constant__ CUtensorMap tm_r,
+// MINB = CTAs per SM the kernel is compiled for.  With two, a thread has 128 registers and the kernel spills (its copies
+// of k~ and r~ leave no shared or tensor memory to park state in); with one it has 224 and spills nothing: a launch with at
+// most one CTA per SM anyway (B*H <= number of SMs) runs 30 % faster in that form, a full one 10 % slower.
+template <int MINB>
+__global__ void __launch_bounds__(256, MINB) chunk_bwd_kernel(const __grid_constant__ CUtensorMap tm_r,
                                                            const __grid_constant__ CUtensorMap tm_k,
                                                            const __grid_constant__ CUtensorMap tm_v,
                                                            const __grid_constant__ CUtensorMap tm_w,

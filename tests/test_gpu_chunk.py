@@ -226,6 +226,26 @@ def test_reference_point_modes(pkg, kind):
         assert scaled_err(np_(got), want) <= TOL_BF16, f"{kind} {name}: {scaled_err(np_(got), want):.3e}"
 
 
+def test_general_backward_full_grid(pkg):
+    """More (batch, head) sequences than SMs, every one with a channel that decays by 250 bits per chunk: the general
+    backward runs in its two-CTAs-per-SM build (smaller problems take the one-per-SM build).  Sampled sequences against
+    the oracle."""
+    from test_gpu_fullsize import check_sampled
+    B, T, H = 5, 192, 32
+    g = torch.Generator(device="cuda").manual_seed(61)
+    mk = lambda sc: (torch.randn(B, T, H * N, generator=g, device="cuda") * sc).to(torch.bfloat16)
+    d = dict(r=mk(0.125), k=mk(0.125), v=mk(0.125), gy=mk(1.0),
+             w=(torch.rand(B, T, H * N, generator=g, device="cuda") * 7 - 6))
+    d["w"].view(B, T, H, N)[..., 7] = 1.0
+    d["w"] = d["w"].to(torch.bfloat16)
+    d["u"] = torch.randn(H, N, generator=g, device="cuda") * 0.1
+    y, _, ck = pkg.forward_raw(d["r"], d["k"], d["v"], d["w"], d["u"], N, want_ckpt=True, variant=pkg.VARIANT_CHUNK)
+    grads = pkg.backward_raw(d["r"], d["k"], d["v"], d["w"], d["u"], d["gy"], N, ckpt=ck, variant=pkg.VARIANT_CHUNK)
+    torch.cuda.synchronize()
+    assert status(pkg) == 0
+    check_sampled(d, [(0, 0), (2, 17), (4, 31)], y, grads)
+
+
 def test_backward_bit_identical_reruns(pkg):
     d = O.make_inputs(2, 256, 2, N, seed=42)
     t = dev_inputs(d)
