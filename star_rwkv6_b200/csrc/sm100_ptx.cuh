@@ -95,6 +95,13 @@ __device__ __forceinline__ void tma_store_5d(const void *tmap, const void *src, 
                  ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(src)), "r"(x), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
                  : "memory");
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while the
+// kernel before it in the stream is still running; it must not touch memory that kernel writes (or reads, if this one
+// writes it) before grid_dependency_wait() returns, which happens when the earlier grid has completed and its writes are
+// visible.  launch_dependents() in the earlier kernel lets the later one be scheduled from that point on.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // untiled bulk copies (16-byte aligned addresses, size a multiple of 16)
 __device__ __forceinline__ void bulk_store(void *gdst, const void *src, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"

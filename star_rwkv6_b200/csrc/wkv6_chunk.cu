@@ -1,5 +1,6 @@
 // Host side of the chunked tensor-core variant: TMA descriptors, launches, workspace sizes.
 #include <atomic>
+#include <utility>
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -22,6 +23,27 @@ static int sm_count() {
         cached[dev].store(n);
     }
     return n;
+}
+
+// Launch with programmatic stream serialization: the kernel's CTAs may become resident while the kernel before it in the
+// stream drains.  A kernel launched this way calls ptx::grid_dependency_wait() before its first access to global
+// memory, so whatever ran before it has completed by then.  Used for the general backward behind the fast one (its
+// launch, which normally finds every flag at zero, then costs 1.5 us instead of 4.5); chaining the other kernels of a
+// split step the same way measured no gain.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_behind(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                                 Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 // Test hook (wkv6_debug_inject): chunk index whose input tiles the forward never requests, -1 = off.
@@ -189,8 +211,7 @@ int chunk_backward_seeded(const wkv6_problem *p, const Dims &d, const void *r, c
     auto general = (int64_t)p->B * p->H <= sm_count() ? chunk_bwd_kernel<1> : chunk_bwd_kernel<2>;
     e = cudaFuncSetAttribute(general, cudaFuncAttributeMaxDynamicSharedMemorySize, ChunkBwdSmem::kAlloc);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(chunk_bwd_kernel)");
-    general<<<p->B * p->H, 256, ChunkBwdSmem::kAlloc, st>>>(mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
-    e = cudaGetLastError();
+    e = launch_behind(general, (unsigned)(p->B * p->H), 256, ChunkBwdSmem::kAlloc, st, mr, mk, mv, mw, mgy, mgr, mgk, mgv, mgw, a);
     return e == cudaSuccess ? WKV6_OK : cuda_fail(e, "chunk_bwd_kernel launch");
 }
 

@@ -187,6 +187,10 @@ __global__ void __launch_bounds__(256, MINB) chunk_bwd_kernel(const __grid_const
         if (threadIdx.x == 0) atomicExch(&g_chunk_status, 50);
         return;
     }
+    // Launched behind the fast kernel with programmatic serialization: its CTAs may already be resident while that
+    // kernel runs; nothing it wrote (the flags first of all) is read before this wait returns.  (Without a kernel before
+    // it in the stream, or without the launch attribute, the wait returns at once.)
+    ptx::grid_dependency_wait();
     if (a.flags != nullptr && a.flags[blockIdx.x] == 0) return;  // the fast kernel has completed this sequence
     uint8_t *sR = smem + SM::oR, *sK = smem + SM::oK, *sV = smem + SM::oV, *sW = smem + SM::oW, *sG = smem + SM::oG;
     uint8_t *sS = smem + SM::oS, *sKH = smem + SM::oKH, *sKD = smem + SM::oKD, *sRD = smem + SM::oRD;

@@ -94,6 +94,9 @@ __global__ void __launch_bounds__(256, 2) chunk_bwd_wide_kernel(const __grid_con
     using SM = WideBwdSmem;
     extern __shared__ __align__(1024) uint8_t wkv6_chunk_smem[];
     uint8_t *const smem = wkv6_chunk_smem;
+    // The general kernel behind this one is launched with programmatic serialization: it may be scheduled from now on
+    // (its CTAs wait for this grid's completion before they read the flags).
+    launch_dependents();
     if ((smem_u32(smem) & 1023u) != 0) {
         if (threadIdx.x == 0) { atomicExch(&g_chunk_status, 50); a.flags[blockIdx.x] = 0; }
         return;
