@@ -78,11 +78,12 @@ WKV6_API const char *wkv6_version(void);
  * reference has no counterpart: its kernels contain no waits. */
 WKV6_API int wkv6_device_status(void);
 
-/* Host-side failure injection for tests of the error path above; no counterpart in the reference.  On the current
- * device, wait_limit_ms > 0 sets the time limit of the in-kernel waits (0 restores one second), and
- * skip_load_chunk >= 0 makes the chunked forward never request the input tiles of that 64-token chunk, so that the
- * wait for them runs out with nothing in flight (-1 restores normal operation).  The kernel then returns normally
- * with wkv6_device_status() != 0; nothing faults, traps or hangs.  Synchronises the device. */
+/* Host-side failure injection for tests of the error path above; no counterpart in the reference.
+ * wait_limit_ms > 0 sets the time limit of the in-kernel waits on the current device (0 restores one second), and
+ * skip_load_chunk >= 0 makes every later launch of the chunked forward (from this process, on any device) never
+ * request the input tiles of that 64-token chunk, so that the wait for them runs out with nothing in flight (-1
+ * restores normal operation).  The kernel then returns normally with wkv6_device_status() != 0; nothing faults,
+ * traps or hangs.  Synchronises the device. */
 WKV6_API int wkv6_debug_inject(int32_t skip_load_chunk, int64_t wait_limit_ms);
 
 /* Which variant AUTO resolves to for this problem (WKV6_VARIANT_SEQ / _CHUNK), or a negative error. */
