@@ -93,6 +93,18 @@ def test_stage_and_copy_argument_checks(L):
     assert lib.wkv6_copy_2d_async(a, 8, a, 16, 16, 4, 0, None) == -1            # destination pitch below the width
     assert lib.wkv6_copy_2d_async(None, 16, a, 16, 16, 4, 0, None) == -1
     assert lib.wkv6_copy_2d_async(None, 0, None, 0, 0, 0, 0, None) == 0          # nothing to copy
+    # the row sum and the scan-only summaries of the sequence-splitting path
+    assert lib.wkv6_sum_rows(a, -1, 64, a, None) == -1
+    assert lib.wkv6_sum_rows(None, 3, 64, a, None) == -1
+    assert lib.wkv6_sum_rows(a, 3, 64, None, None) == -1
+    assert lib.wkv6_sum_rows(None, 0, 0, None, None) == 0                        # nothing to sum
+    pb = _problem(L, B=6, T=128, x_dtype=L.BF16, y_dtype=L.BF16)
+    assert lib.wkv6_segment_summary_for_scan(ctypes.byref(pb), a, a, a, 0, 4, a, a, None) == -1   # 6 rows are not 4 segments each
+    assert b"multiple" in lib.wkv6_last_error()
+    assert lib.wkv6_segment_summary_for_scan(ctypes.byref(pb), a, a, a, 0, 0, a, a, None) == -1
+    assert lib.wkv6_segment_summary_for_scan(ctypes.byref(pb), None, a, a, 0, 3, a, a, None) == -1
+    pf = _problem(L, B=6, T=128)                                                 # fp32: no chunked variant
+    assert lib.wkv6_segment_summary_for_scan(ctypes.byref(pf), a, a, a, 0, 3, a, a, None) == -2
 
 
 def test_missing_library_fails_loudly():
