@@ -80,6 +80,49 @@ class OracleBackend:
         return tuple(torch.tensor(x.reshape(sh)) for x in (gr, gk, gv, gw)) + (torch.tensor(gu),)
 
 
+class LeanOracleBackend(OracleBackend):
+    """The same backend offering the scan-only summaries: the segment no exclusive scan reads (the last of a sequence going
+    forward, the first in reverse) comes back as NaN, so any use of it poisons the results."""
+    scan_only_summaries = True
+
+    def summary(self, x1, x2, w, reverse, scan_only_segments=0):
+        S, dec = super().summary(x1, x2, w, reverse)
+        if scan_only_segments > 0:
+            G = scan_only_segments
+            rows = torch.arange(S.shape[0]) % G == (0 if reverse else G - 1)
+            S[rows] = float("nan")
+            dec[rows] = float("nan")
+        return S, dec
+
+    def scan(self, B, H, G, dec, state, s0, reverse):
+        # like the library's kernel, the scan folds the last summary it walks over only into the state it returns second
+        out, last = super().scan(B, H, G, torch.nan_to_num(dec, nan=0.0), torch.nan_to_num(state, nan=0.0), s0, reverse)
+        assert not torch.isnan(out).any()
+        return out, last
+
+
+@pytest.mark.parametrize("G", [2, 3])
+def test_lean_orchestration_single_rank(G):
+    """need_last=False on one rank: no final state comes back, the skipped summaries are never needed, and the backward takes
+    its decays from the reverse summaries.  The NaN rows must not reach a result... and, to make sure the scan is not fed a
+    wrong row instead, the scan of this backend replaces only NaN by zero: a misplaced skip would change the numbers."""
+    from star_rwkv6_b200 import segments as seg
+    B, T, H, N = 2, 24, 2, 8
+    d = O.make_inputs(B, T, H, N, seed=6)
+    full = {n: torch.tensor(d[n], dtype=torch.float64) for n in ("r", "k", "v", "w", "gy")}
+    u = torch.tensor(d["u"], dtype=torch.float64)
+    be = LeanOracleBackend(N)
+    y, last, ctx = seg.segmented_forward(be, full["r"], full["k"], full["v"], full["w"], u, G, want_ckpt=True, need_last=False)
+    assert last is None and ctx["lean"]
+    g = seg.segmented_backward(be, ctx, full["r"], full["k"], full["v"], full["w"], u, full["gy"])
+    yo, _ = O.wkv6_forward(d["r"], d["k"], d["v"], d["w"], d["u"], N)
+    go = O.wkv6_backward(d["r"], d["k"], d["v"], d["w"], d["u"], d["gy"], N)
+    assert np.allclose(y.numpy(), yo, rtol=1e-10, atol=1e-12)
+    for a, b in zip(g[:4], go[:4]):
+        assert np.allclose(a.numpy(), b, rtol=1e-9, atol=1e-11)
+    assert np.allclose(g[4].numpy(), go[4].sum(0), rtol=1e-9, atol=1e-11)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
