@@ -11,6 +11,7 @@ calls themselves go straight to the C ABI and allocate nothing.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 from typing import Dict, Optional
 
@@ -43,8 +44,15 @@ class HostPipeline:
                 s["gu"] = torch.empty((rows_per_slice, H, head_size), dtype=torch.float32, device=self.device)
                 s["stream"] = torch.cuda.Stream(self.device)
                 self.slots.append(s)
-            self.u = torch.empty((H, head_size), dtype=torch.float32, device=self.device)
+            # two copies of u and a stream of their own for its upload, so that a call submitted while the one before is
+            # still running neither overwrites the u that call reads nor waits for it
+            self.u2 = [torch.empty((H, head_size), dtype=torch.float32, device=self.device) for _ in range(2)]
+            self.u = self.u2[0]
+            self.ctl = torch.cuda.Stream(self.device)
             self.gu_sum = torch.zeros((H, head_size), dtype=torch.float32, device=self.device)
+            self._calls = 0
+            self._tickets = collections.deque()
+            self._gu_parts = {}   # (call parity, slices) -> [slices, H, N]: one row per slice, summed in slice order at the end
             p = make_problem(self.slots[0]["r"], self.u, head_size, ydt, variant)
             ck, ws = lib.wkv6_ckpt_bytes(ctypes.byref(p)), lib.wkv6_backward_workspace_bytes(ctypes.byref(p), 1)
             for s in self.slots:
@@ -80,27 +88,50 @@ class HostPipeline:
     def fwd_bwd(self, r, k, v, w, u, gy, out: Optional[Dict[str, torch.Tensor]] = None):
         """r, k, v, w, gy: [B,T,C] host tensors (pinned, so that the copies overlap); u: [H,N] fp32.  Fills / returns
         ``out`` (host tensors y, gr, gk, gv, gw) and returns gu [H,N] fp32 on the host.  Synchronises before returning."""
+        return self.wait(self.submit(r, k, v, w, u, gy, out=out))
+
+    def wait(self, ticket):
+        """Block until the call that returned ``ticket`` has delivered: (out, gu) with every tensor complete in host memory."""
+        done, out, gu_host = ticket
+        done.synchronize()
+        return out, gu_host
+
+    def submit(self, r, k, v, w, u, gy, out: Optional[Dict[str, torch.Tensor]] = None):
+        """``fwd_bwd`` without the final synchronisation: everything is queued and a ticket for ``wait`` comes back.  A loop
+        that submits call i + 1 before it waits for call i (with its own ``out`` tensors per call in flight) keeps both copy
+        engines busy across the boundary between the calls: the copies back of the last rows of one call run beside the
+        copies in of the first rows of the next.  The inputs of a call must stay untouched until its ticket has been waited for."""
         B, T, C = r.shape
         assert T == self.T and C == self.H * self.N
         host = dict(zip(_IN, (r, k, v, w, gy)))
         if out is None:
             out = {n: torch.empty(tuple(r.shape), dtype=self.slots[0][n].dtype).pin_memory() for n in _OUT}
         main = torch.cuda.current_stream(self.device)
+        while len(self._tickets) >= 2:   # at most two calls in flight: the u and gu staging buffers are reused after that
+            self._tickets.popleft().synchronize()
+        ub = self.u2[self._calls & 1]
+        gu_host = torch.empty((self.H, self.N), dtype=torch.float32, pin_memory=True)   # this call's own landing buffer
+        self._calls += 1
         with torch.cuda.device(self.device):
-            self.u.copy_(u, non_blocking=True)
-            self.gu_sum.zero_()
+            work = self.slices(B)
+            key = ((self._calls - 1) & 1, len(work))
+            if key not in self._gu_parts:
+                self._gu_parts[key] = torch.empty((len(work), self.H, self.N), dtype=torch.float32, device=self.device)
+            parts = self._gu_parts[key]
             ready = torch.cuda.Event()
-            ready.record(main)
-            for i, (b0, b1, h0, h1) in enumerate(self.slices(B)):
+            with torch.cuda.stream(self.ctl):
+                ub.copy_(u, non_blocking=True)
+                parts.zero_()
+                ready.record(self.ctl)
+            for i, (b0, b1, h0, h1) in enumerate(work):
                 n, g = b1 - b0, h1 - h0
                 s = self.slots[i % len(self.slots)]
                 # the slot's buffers, viewed as dense [n, T, g*N] tensors
                 d = {name: s[name].view(-1)[: n * T * g * self.N].view(n, T, g * self.N) for name in _IN + _OUT}
                 gu = s["gu"].view(-1)[: n * g * self.N].view(n, g, self.N)
-                u_g = self.u[h0:h1]
+                u_g = ub[h0:h1]
                 with torch.cuda.stream(s["stream"]):
-                    if i < len(self.slots):
-                        s["stream"].wait_event(ready)
+                    s["stream"].wait_event(ready)
                     st = _stream(self.device)
                     for name in _IN:
                         self._copy(d[name], host[name], b0, b1, h0, h1, 0, st)
@@ -112,15 +143,15 @@ class HostPipeline:
                                             _ptr(gu), _ptr(s["ckpt"]), _ptr(s["ws"]), s["ws_bytes"], st))
                     for name in _OUT:
                         self._copy(d[name], out[name], b0, b1, h0, h1, 1, st)
-                    s["gu_part"] = gu.sum(0)
-                    done = torch.cuda.Event()
-                    done.record(s["stream"])
-                # the running sum of gu is kept on the main stream, in slice order (fixed order: reruns are bit-identical)
-                main.wait_event(done)
-                self.gu_sum[h0:h1] += s["gu_part"]
+                    torch.sum(gu, dim=0, out=parts[i, h0:h1])   # this slice's row of gu (its head group; the rest stays zero)
             for s in self.slots:
                 main.wait_stream(s["stream"])
-            return out, self.gu_sum.to("cpu")
+            torch.sum(parts, dim=0, out=self.gu_sum)   # one reduction over the slices, the same order in every run
+            gu_host.copy_(self.gu_sum, non_blocking=True)
+            done_all = torch.cuda.Event()
+            done_all.record(main)
+            self._tickets.append(done_all)
+            return done_all, out, gu_host
 
 
 def fwd_bwd_host(r, k, v, w, u, gy, head_size: int, out=None, device=None, rows_per_slice: int = 1, slots: int = 6,

@@ -53,3 +53,25 @@ def test_host_pipeline_head_groups(B):
         assert torch.equal(out2[name], want.cpu()), name
     assert torch.allclose(gu, gub.sum(0).cpu(), rtol=1e-5, atol=1e-6)
     assert torch.allclose(gu2, gub.sum(0).cpu(), rtol=1e-5, atol=1e-6)
+
+
+def test_calls_in_flight():
+    """submit / wait with several calls in flight (different inputs and different u per call, separate output tensors per
+    call, more calls than the pipeline keeps in flight): every call delivers exactly what the same call made alone delivers."""
+    from star_rwkv6_b200.host import HostPipeline
+    B, T, H, N = 3, 128, 4, 64
+    g = torch.Generator().manual_seed(7)
+    mk = lambda s: (torch.randn(B, T, H * N, generator=g) * s).to(torch.bfloat16).pin_memory()
+    calls = []
+    for i in range(5):
+        calls.append(dict(r=mk(0.125), k=mk(0.125), v=mk(0.125), gy=mk(1.0),
+                          w=(torch.rand(B, T, H * N, generator=g) * 7 - 6).to(torch.bfloat16).pin_memory(),
+                          u=torch.randn(H, N, generator=g) * 0.1))
+    pipe = HostPipeline(T, H, N, slots=3)
+    alone = [pipe.fwd_bwd(c["r"], c["k"], c["v"], c["w"], c["u"], c["gy"]) for c in calls]
+    tickets = [pipe.submit(c["r"], c["k"], c["v"], c["w"], c["u"], c["gy"]) for c in calls]   # all five queued, then collected
+    for i, t in enumerate(tickets):
+        out, gu = pipe.wait(t)
+        for name in ("y", "gr", "gk", "gv", "gw"):
+            assert torch.equal(out[name], alone[i][0][name]), (i, name)
+        assert torch.equal(gu, alone[i][1]), i
