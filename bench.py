@@ -541,6 +541,7 @@ def run_b200(a):
 
         op_ms, n_e2e = timed(e2e_step)
         call_ms, _ = timed(host_step)
+        pipe.ramp = False   # with the next step's fill beside this step's drain, whole rows (plain copies) are faster than head groups
         e2e_ms, _ = timed_two_in_flight()
         esz = 2 if a.dtype == "bf16" else 4
         e2e = {"value": tokens_per_step_global / (e2e_ms * 1e-3) / 1e6, "unit": UNIT,

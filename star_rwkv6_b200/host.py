@@ -28,8 +28,10 @@ _OUT = ("y", "gr", "gk", "gv", "gw")
 class HostPipeline:
     def __init__(self, T: int, H: int, head_size: int, dtype=torch.bfloat16, device=None, rows_per_slice: int = 1,
                  slots: int = 6, variant: int = _lib.VARIANT_AUTO, ramp: bool = True):
-        """``ramp``: cut the first and the last batch row into two head groups (heads are as independent as rows), so
-        that the first kernels start and the last copy back ends half a row's transfer earlier.  Measured at B8 T4096
+        """``ramp`` (an attribute, may be changed between calls): cut the first and the last batch row into two head groups
+        (heads are as independent as rows), so that the first kernels start and the last copy back ends half a row's transfer
+        earlier - for one call at a time; a loop that keeps two calls in flight (``submit`` / ``wait``) is faster without it
+        (14.7 against 15.3 ms per call at the same shape: the next call's fill covers the drain, and whole rows are plain copies).  Measured at B8 T4096
         H32 with six slots: 17.0 ms per call against 17.4 ms without (same GPU, alternating runs); finer groups (eighths) were slower, their pitched copies being short."""
         self.device = torch.device(device if device is not None else "cuda")
         self.T, self.H, self.N, self.rows, self.variant = T, H, head_size, rows_per_slice, variant
