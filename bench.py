@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--B", type=int, default=8)
     ap.add_argument("--T", type=int, default=4096)
+    ap.add_argument("--fast-channel", type=float, default=None,
+                    help="not the benchmark distribution: channel 5 of every head gets this constant w (1.0 = 250 bits of decay "
+                         "per chunk, which sends every sequence to the per-block reference points and the general backward)")
     ap.add_argument("--H", type=int, default=32)
     ap.add_argument("--N", type=int, default=64)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
@@ -81,7 +84,8 @@ def parse():
 
 
 def workload_name(a):
-    return f"wkv6 fwd+bwd B{a.B} T{a.T} H{a.H} N{a.N} {a.dtype}"
+    extra = f", channel 5 of every head at w = {a.fast_channel}" if getattr(a, "fast_channel", None) is not None else ""
+    return f"wkv6 fwd+bwd B{a.B} T{a.T} H{a.H} N{a.N} {a.dtype}{extra}"
 
 
 # ---- CPU baseline / reference arm -----------------------------------------------------------------
@@ -266,12 +270,17 @@ def _scaled_err(a, b):
     return float((a.float() - b.float()).abs().max()) / (den if den > 0 else 1.0)
 
 
+FAST_CHANNEL_W = None   # --fast-channel: one channel per head gets this constant w (a decay spectrum with a fast channel)
+
+
 def _device_inputs(torch, dev, B, T, C, H, N, xdt, seed):
     """One seeded input set, generated on the device (the same values on every rank for the same seed)."""
     g = torch.Generator(device=dev).manual_seed(seed)
     mk = lambda s: (torch.randn(B, T, C, generator=g, device=dev) * s).to(xdt)
-    d = {"r": mk(N ** -0.5), "k": mk(N ** -0.5), "v": mk(N ** -0.5),
-         "w": (torch.rand(B, T, C, generator=g, device=dev) * 7.0 - 6.0).to(xdt), "gy": mk(1.0)}
+    w = torch.rand(B, T, C, generator=g, device=dev) * 7.0 - 6.0
+    if FAST_CHANNEL_W is not None:
+        w.view(B, T, H, N)[..., 5] = FAST_CHANNEL_W
+    d = {"r": mk(N ** -0.5), "k": mk(N ** -0.5), "v": mk(N ** -0.5), "w": w.to(xdt), "gy": mk(1.0)}
     u = torch.randn(H, N, generator=g, device=dev) * 0.1
     return d, u
 
@@ -279,6 +288,8 @@ def _device_inputs(torch, dev, B, T, C, H, N, xdt, seed):
 def run_b200(a):
     import torch
     import torch.distributed as dist
+    global FAST_CHANNEL_W
+    FAST_CHANNEL_W = a.fast_channel
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
