@@ -69,5 +69,25 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_variant(out_path: str, extra_flags) -> str:
+    """The same library compiled with extra nvcc flags (e.g. ``-DWKV6_TIMING``: phase stamps inside the chunked kernels and
+    the exports that read them) into ``out_path``; objects go to a temporary directory, the in-tree library is untouched.
+    ``WKV6_B200_LIB=<out_path>`` makes the package load it."""
+    import tempfile
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    with tempfile.TemporaryDirectory() as tmp:
+        procs, objs = [], []
+        for src in sources():
+            obj = os.path.join(tmp, os.path.splitext(os.path.basename(src))[0] + ".o")
+            cmd = [nvcc] + NVCC_FLAGS + list(extra_flags) + ["-c", src, "-o", obj]
+            procs.append((cmd, subprocess.Popen(cmd)))
+            objs.append(obj)
+        for cmd, pr in procs:
+            if pr.wait() != 0:
+                raise RuntimeError("nvcc failed: " + " ".join(cmd))
+        subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", out_path] + objs + ["-lcudart"])
+    return out_path
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

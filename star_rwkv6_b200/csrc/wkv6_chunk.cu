@@ -334,4 +334,7 @@ extern "C" __attribute__((visibility("default"))) int wkv6_debug_timing(long lon
 extern "C" __attribute__((visibility("default"))) int wkv6_debug_cta_times(long long *out) {
     return (int)cudaMemcpyFromSymbol(out, wkv6::g_cta_times, sizeof(long long) * 1024 * 8);
 }
+extern "C" __attribute__((visibility("default"))) int wkv6_debug_cta_sm(int *out) {
+    return (int)cudaMemcpyFromSymbol(out, wkv6::g_cta_sm, sizeof(int) * 1024);
+}
 #endif

@@ -54,8 +54,15 @@ __device__ int g_chunk_status;
 // Phase timestamps of CTA 0 (builds with -DWKV6_TIMING only): g_chunk_timing[chunk][phase][warp] = clock64() of lane 0
 #ifdef WKV6_TIMING
 __device__ long long g_chunk_timing[64][16][8];
-__device__ long long g_cta_times[1024][8];  // per CTA: four globaltimer stamps (entry, loop start, loop end, exit)
-#define WKV6_CSTAMP(k) do { if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta_times[blockIdx.x][(k)] = (long long)ptx::global_timer_ns(); } while (0)
+__device__ long long g_cta_times[1024][8];  // per CTA: eight %globaltimer stamps from entry (0) to exit (7)
+__device__ int g_cta_sm[1024];              // per CTA: the SM it ran on
+#define WKV6_CSTAMP(k) \
+    do { \
+        if (threadIdx.x == 0 && blockIdx.x < 1024) { \
+            g_cta_times[blockIdx.x][(k)] = (long long)ptx::global_timer_ns(); \
+            if ((k) == 0) { unsigned sm_; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_)); g_cta_sm[blockIdx.x] = (int)sm_; } \
+        } \
+    } while (0)
 #define WKV6_TSTAMP(iter, k) \
     do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (iter) < 64) g_chunk_timing[(iter)][(k)][threadIdx.x >> 5] = clock64(); } while (0)
 #else
